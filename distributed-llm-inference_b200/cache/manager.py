@@ -38,6 +38,7 @@ class GroupSpec:
 
     num_pages: int
     window: int | None = None
+    keep_first: int = 0  # with a window: the first tokens of a sequence stay visible, their pages are never given back
 
 
 @dataclass(frozen=True)
@@ -351,7 +352,7 @@ class CacheManager:
                 continue
             # the next query sits at position >= num_computed and reads keys > position - window
             dead_pages = max(0, (num_computed - group.window + 1) // ps)
-            for j in range(min(dead_pages, len(table))):
+            for j in range(-(-group.keep_first // ps), min(dead_pages, len(table))):
                 if table[j] >= 0:
                     pool.release(table[j])
                     table[j] = -1
@@ -424,5 +425,6 @@ class CacheManager:
                         w = self.groups[g].window
                         assert w is not None and (j + 1) * self.page_size - 1 <= req.num_computed - w, \
                             "a page still inside the window was given back"
+                        assert j * self.page_size >= self.groups[g].keep_first, "a page of the kept first tokens was given back"
                 assert self._mirror[g][req.slot, : len(table)].tolist() == table, "the table array differs from the table"
             pool.check(expected)

@@ -21,6 +21,9 @@ class PagedKVNeed:
     window: int | None = None
     # the values are read from the keys' rows (their leading numbers): no value pool is kept, ``LayerCache.v`` is ``k``
     values_in_keys: bool = False
+    value_dim: int | None = None  # size of a value row where it differs from ``head_dim`` (None: the same)
+    # with a window: the sequence's first ``keep_first`` tokens stay visible, so the pages that hold them are never given back
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

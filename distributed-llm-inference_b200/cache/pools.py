@@ -51,9 +51,16 @@ def plan_groups(needs: list, run_order) -> tuple[list[PagedKVNeed], list[int | N
     return groups, of_step
 
 
+class LayerCaches(list):
+    """The run steps' ``LayerCache``s in run order, and beside them ``embedding``: the state slots of an embedding that
+    keeps something per request (None when it keeps nothing)."""
+
+    embedding: LayerCache | None = None
+
+
 class CachePools:
     def __init__(self, needs: list, run_order, pages_per_group: list[int], page_size: int, max_requests: int,
-                 dtype: torch.dtype, device: torch.device | str) -> None:
+                 dtype: torch.dtype, device: torch.device | str, embedding_need=None) -> None:
         self.page_size = page_size
         self.group_needs, self.group_of_step = plan_groups(needs, run_order)
         if len(pages_per_group) != len(self.group_needs):
@@ -68,10 +75,14 @@ class CachePools:
         self.scratch_pages = list(pages_per_group)
         for need, pages, own in zip(self.group_needs, pages_per_group, owners):
             shape = (len(own), pages + 1, need.num_kv_heads, page_size, need.head_dim)
+            v_shape = shape[:-1] + (need.value_dim or need.head_dim,)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(self.k[-1] if need.values_in_keys else torch.zeros(shape, dtype=dtype, device=device))
+            self.v.append(self.k[-1] if need.values_in_keys else torch.zeros(v_shape, dtype=dtype, device=device))
         self.scratch_state_slot = max_requests
-        self.layer_caches: list[LayerCache] = []
+        self.layer_caches: LayerCaches = LayerCaches()
+        if state_needs_of(embedding_need):
+            self.layer_caches.embedding = LayerCache(states=tuple(
+                torch.zeros((max_requests + 1, *need.shape), dtype=need.dtype, device=device) for need in state_needs_of(embedding_need)))
         for i, answer in enumerate(needs):
             src = run_order[i].cache_of
             if src is not None:
@@ -89,12 +100,16 @@ class CachePools:
 
     @property
     def has_state(self) -> bool:
-        return any(c.states for c in self.layer_caches)
+        return any(c.states for c in self._all_caches())
+
+    def _all_caches(self):
+        extra = self.layer_caches.embedding
+        return [*self.layer_caches, *([extra] if extra is not None else [])]
 
     def reset_state(self, slot: int) -> None:
         """Zero a slot's state in every layer: a request starts (or starts over) from nothing."""
         seen = set()
-        for c in self.layer_caches:
+        for c in self._all_caches():
             for state in c.states:
                 if state.data_ptr() not in seen:
                     seen.add(state.data_ptr())
@@ -108,5 +123,6 @@ class CachePools:
         for i, answer in enumerate(needs):
             need = paged_need_of(answer)
             if need is not None and run_order[i].cache_of is None:
-                out[group_of_step[i]] += (1 if need.values_in_keys else 2) * need.num_kv_heads * page_size * need.head_dim * dtype.itemsize
+                row = need.head_dim + (0 if need.values_in_keys else (need.value_dim or need.head_dim))
+                out[group_of_step[i]] += need.num_kv_heads * page_size * row * dtype.itemsize
         return out

@@ -14,6 +14,7 @@ from typing import Any, Callable
 
 from .llama import LlamaConfig, UnsupportedModelError, llama_model_spec
 from .pazenex import PazenexConfig, pazenex_model_spec
+from .pokadra import PokadraConfig, pokadra_model_spec
 from .spec import ModelSpec
 from .sugonex import SugonexConfig, sugonex_model_spec
 
@@ -62,3 +63,4 @@ register_architecture(
 )
 register_architecture(Architecture("Pazenex", PazenexConfig.from_dict, pazenex_model_spec))
 register_architecture(Architecture("Sugonex", SugonexConfig.from_dict, sugonex_model_spec))
+register_architecture(Architecture("Pokadra", PokadraConfig.from_dict, pokadra_model_spec))

@@ -548,14 +548,23 @@ __device__ __forceinline__ void gate_up_columns(int i, int I, int tiled, int& g,
   }
 }
 
-// what a gated feed-forward applies to its gate: 0 silu, 1 gelu with the tanh approximation
+// what a gated feed-forward applies to its gate: 0 silu, 1 gelu with the tanh approximation, 2 g * sigmoid(1.702 g)
 __device__ __forceinline__ float glu_activation(float g, int act) {
   if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  if (act == 2) return g / (1.f + expf(-1.702f * g));
   return g / (1.f + expf(-g));
+}
+// act(min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0: no bounds
+__device__ __forceinline__ float glu_value(float g, float u, int act, float limit, float shift) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return glu_activation(g, act) * (u + shift);
 }
 
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I, int tiled, int act) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int n, int I, int tiled, int act, float limit, float shift) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)n * I;
@@ -566,12 +575,13 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     gate_up_columns(i, I, tiled, gc, uc);
     const float g = to_float(gu[t * 2 * I + gc]);
     const float u = to_float(gu[t * 2 * I + uc]);
-    out[idx] = from_float<T>(glu_activation(g, act) * u);
+    out[idx] = from_float<T>(glu_value(g, u, act, limit, shift));
   }
 }
 
 // bfloat16, I % 8 == 0: one 16-byte load of gate and of up, one 16-byte store, per thread
-__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I, int tiled, int act) {
+__global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I, int tiled, int act,
+                                         float limit, float shift) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.y;
@@ -588,26 +598,27 @@ __global__ void silu_mul_bf16_vec_kernel(__nv_bfloat16* __restrict__ out, const 
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const float2 a = __bfloat1622float2(gp[k]), b = __bfloat1622float2(up[k]);
-    rp[k] = __floats2bfloat162_rn(glu_activation(a.x, act) * b.x, glu_activation(a.y, act) * b.y);
+    rp[k] = __floats2bfloat162_rn(glu_value(a.x, b.x, act, limit, shift), glu_value(a.y, b.y, act, limit, shift));
   }
   reinterpret_cast<uint4*>(out + (size_t)t * I)[i] = r;
 }
 
-DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, int act, int dtype, cudaStream_t stream) {
-  if ((tiled && (I % 64)) || act < 0 || act > 1) return DLI_ERR_UNSUPPORTED;
+DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, int act, float limit, float shift, int dtype,
+                            cudaStream_t stream) {
+  if ((tiled && (I % 64)) || act < 0 || act > 2) return DLI_ERR_UNSUPPORTED;
   if (n == 0) return 0;
   if (dtype == DLI_BF16 && I % 8 == 0 && n <= 65535) {
     dim3 grid((I / 8 + 255) / 256, n);
-    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, tiled, act);
+    launch_pdl((silu_mul_bf16_vec_kernel), dim3(grid), dim3(256), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, tiled, act, limit, shift);
     return (int)cudaGetLastError();
   }
   const size_t total = (size_t)n * I;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < (size_t)sm_count() * 16 ? (total + threads - 1) / threads : (size_t)sm_count() * 16);
   if (dtype == DLI_F32)
-    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I, tiled, act);
+    launch_pdl((silu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, 1, (float*)out, (const float*)gu, n, I, tiled, act, limit, shift);
   else
-    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I, tiled, act);
+    launch_pdl((silu_mul_kernel<__nv_bfloat16>), dim3(blocks), dim3(threads), 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, n, I, tiled, act, limit, shift);
   return (int)cudaGetLastError();
 }
 

@@ -80,11 +80,13 @@ class ModelRunner:
         order = model.spec.run_order
         n_groups = len({paged_need_of(n) for n in needs} - {None})
         pages = [num_pages] * n_groups if isinstance(num_pages, int) else list(num_pages)
-        self.pools = CachePools(needs, order, pages, page_size, max_requests, model.dtype, model.device)
+        embedding_need = model.embedding_need()
+        self.pools = CachePools(needs, order, pages, page_size, max_requests, model.dtype, model.device, embedding_need=embedding_need)
         self.manager = CacheManager(
-            [GroupSpec(p, need.window) for p, need in zip(pages, self.pools.group_needs)],
+            [GroupSpec(p, need.window, need.keep_first if need.window is not None else 0) for p, need in zip(pages, self.pools.group_needs)],
             page_size, max_requests, enable_prefix_caching=enable_prefix_caching,
-            has_state=any(state_needs_of(n) for n in needs), watermark=watermark, eviction_policy=eviction_policy,
+            has_state=any(state_needs_of(n) for n in needs) or bool(state_needs_of(embedding_need)), watermark=watermark,
+            eviction_policy=eviction_policy,
         )
         self.page_size = page_size
         self.uploader = Uploader(model.device)

@@ -113,3 +113,12 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
     elif total > singles:
         ops.paged_attention_mma(out, qkv, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, singles,
                                 total - singles, batch.max_q_len, singles, num_heads, scale, window, sink=sink)
+
+
+def diff_attention(out: torch.Tensor, q: torch.Tensor, cache, batch, gate: torch.Tensor | None, num_heads: int, scale: float,
+                   window: int | None, keep_first: int, lam: float, post: float, eps: float) -> None:
+    """Differential attention of every token of the step over its sequence's pages (``ops.diff_attention_simt`` says what is
+    computed)."""
+    group = batch.group(cache.group)
+    ops.diff_attention_simt(out, q, cache.k, cache.v, group.block_tables, batch.seq_of_token, batch.positions, gate, num_heads, scale,
+                            window, keep_first, lam, post, eps)

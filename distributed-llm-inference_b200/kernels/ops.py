@@ -216,18 +216,22 @@ def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tenso
     return table
 
 
-GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # what a gated feed-forward may apply to its gate
+# what a gated feed-forward may apply to its gate; quick_gelu(g) = g * sigmoid(1.702 g)
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "quick_gelu": 2}
 
 
-def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, tiled: bool = False, activation: str = "silu") -> None:
-    """out[n, I] = act(gate) * up, act = silu or another of GLU_ACTIVATIONS.  gate_up [n, 2 I] holds gate | up side by
+def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, tiled: bool = False, activation: str = "silu", limit: float = 0.0,
+             up_shift: float = 0.0) -> None:
+    """out[n, I] = act(gate) * (up + up_shift), act = silu or another of GLU_ACTIVATIONS; with ``limit`` > 0 the gate is
+    bounded from above by it and up to [-limit, limit] first.  gate_up [n, 2 I] holds gate | up side by
     side, or, ``tiled`` (I a multiple of 64), blocks of 128 columns: 64 gate features, then the same 64 up features."""
     _need(out, "out"), _need(gate_up, "gate_up", out.dtype)
     n, I = out.shape
     if out.dtype not in DT_CODE or tuple(gate_up.shape) != (n, 2 * I) or (tiled and I % 64) or activation not in GLU_ACTIVATIONS:
         raise KernelError("silu_mul: shapes, dtype or activation do not agree")
-    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(gate_up), n, I, int(tiled), GLU_ACTIVATIONS[activation], DT_CODE[out.dtype], _stream()), "silu_mul")
+    f = _fn("elementwise.cu", "dli_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(gate_up), n, I, int(tiled), GLU_ACTIVATIONS[activation], float(limit), float(up_shift), DT_CODE[out.dtype],
+             _stream()), "silu_mul")
 
 
 def add_rmsnorm_pair(y1: torch.Tensor, y2: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor | None, b: torch.Tensor | None,
@@ -1165,3 +1169,154 @@ def delta_rule_scan(o: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: 
            "delta_rule_scan")
     global launch_count
     launch_count += 2 if (max_len > 4 and d % 4 == 0 and dv % 4 == 0) else 1  # three kernels for portions, two for a decode step
+
+
+# ------------------------------------------------------------------ a stream whose sublayers are normed on their output
+
+
+def pair_embedding(h: torch.Tensor, table: torch.Tensor, scale: float, pair_table: torch.Tensor | None, buckets: int, mul_prev: int, mul_cur: int,
+                   ids: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor,
+                   prev_state: torch.Tensor | None, y: torch.Tensor | None = None) -> None:
+    """h[t] = table[ids[t]] * scale + pair_table[row(t)], float32.  row(t) = (prev * mul_prev + ids[t] * mul_cur) mod buckets, prev
+    the token in front of t in its sequence; row ``buckets`` (the table's last) for a token at position 0.  The token in front of
+    a sequence's first row of this step is prev_state[state_slot[s]] (int32 [slots]), where the step's last token is left for
+    the next step.  Without ``pair_table`` only the first term.  With ``y`` (the tables' dtype) h is also written there, rounded once."""
+    _need(h, "h", torch.float32), _need(table, "table"), _need(ids, "ids", torch.int32)
+    n, H = h.shape
+    if table.shape[1] != H or ids.numel() != n or table.dtype not in DT_CODE:
+        raise KernelError("pair_embedding: shapes or dtype do not agree")
+    if pair_table is not None:
+        _need(pair_table, "pair_table", table.dtype), _need(prev_state, "prev_state", torch.int32)
+        if tuple(pair_table.shape) != (buckets + 1, H):
+            raise KernelError("pair_embedding: the pair table has buckets + 1 rows")
+    f = _fn("residual_ops.cu", "dli_pair_embedding", [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    if y is not None and (y.dtype != table.dtype or y.shape != h.shape or not y.is_contiguous()):
+        raise KernelError("pair_embedding: y has h's shape and the tables' dtype")
+    _check(f(_ptr(h), _ptr(table), float(scale), _ptr(pair_table), int(buckets), int(mul_prev), int(mul_cur), _ptr(ids), _ptr(positions),
+             _ptr(seq_of_token), _ptr(q_start), _ptr(state_slot), _ptr(prev_state), _ptr(y), n, H, DT_CODE[table.dtype], _stream()), "pair_embedding")
+
+
+def group_norm_add(h: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, mult: float,
+                   y: torch.Tensor | None = None) -> None:
+    """h += mult * norm(a) * weight, norm = each of ``groups`` equal consecutive parts of a row divided by its own root mean
+    square (eps inside the root); float32.  With ``y`` (a's dtype) the new h is also written there, rounded once."""
+    _need(h, "h", torch.float32), _need(a, "a"), _need(weight, "weight", torch.float32)
+    n, H = h.shape
+    if tuple(a.shape) != (n, H) or weight.numel() != H or a.dtype not in DT_CODE or H % groups or (y is not None and (y.dtype != a.dtype or y.shape != a.shape)):
+        raise KernelError("group_norm_add: shapes or dtype do not agree")
+    if y is not None:
+        _need(y, "y")
+    f = _fn("residual_ops.cu", "dli_group_norm_add", [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(h), _ptr(a), _ptr(weight), int(groups), float(eps), float(mult), _ptr(y), n, H, DT_CODE[a.dtype], _stream()), "group_norm_add")
+
+
+def group_norm_rows(y: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, rows: torch.Tensor | None = None) -> None:
+    """y[i] = norm(h[rows[i]]) * weight (rows None: every row), the norm of ``group_norm_add``."""
+    _need(y, "y"), _need(h, "h", torch.float32), _need(weight, "weight", torch.float32)
+    n, H = y.shape
+    if h.shape[1] != H or y.dtype not in DT_CODE or H % groups or (rows is None and h.shape[0] != n) or (rows is not None and rows.numel() != n):
+        raise KernelError("group_norm_rows: shapes or dtype do not agree")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    f = _fn("residual_ops.cu", "dli_group_norm_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(h), _ptr(weight), _ptr(rows), int(groups), float(eps), n, H, DT_CODE[y.dtype], _stream()), "group_norm_rows")
+
+
+def gelu_mul_rows(g: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor) -> None:
+    """g[t, j] = gelu_tanh(g[t, j]) * table[ids[t], col0 + j], in place (float32 arithmetic)."""
+    _need(g, "g"), _need(table, "table", g.dtype), _need(ids, "ids", torch.int32)
+    n, dim = g.shape
+    if g.dtype not in DT_CODE or ids.numel() != n or col0 < 0 or col0 + dim > table.shape[1]:
+        raise KernelError("gelu_mul_rows: shapes or dtype do not agree")
+    f = _fn("residual_ops.cu", "dli_gelu_mul_rows", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(g), _ptr(table), table.shape[1], int(col0), _ptr(ids), n, dim, DT_CODE[g.dtype], _stream()), "gelu_mul_rows")
+
+
+def depth_average(out: torch.Tensor, x0: torch.Tensor, hist: torch.Tensor, weights: torch.Tensor, count: int, y: torch.Tensor | None = None) -> None:
+    """out = weights[0] * x0 + sum over 1 <= j < count of weights[j] * hist[j - 1] (x0, out [n, H] and hist [slots, n, H] float32;
+    out may be a slot of hist beyond the ones read).  With ``y`` the result is also written there in y's dtype."""
+    _need(out, "out", torch.float32), _need(x0, "x0", torch.float32), _need(hist, "hist", torch.float32), _need(weights, "weights", torch.float32)
+    if hist.dim() != 3 or tuple(hist.shape[1:]) != tuple(out.shape) or x0.shape != out.shape or not 1 <= count <= hist.shape[0] + 1 or weights.numel() < count:
+        raise KernelError("depth_average: shapes do not agree")
+    if y is not None:
+        _need(y, "y")
+        if y.dtype not in DT_CODE or y.shape != out.shape:
+            raise KernelError("depth_average: y has out's shape")
+    f = _fn("residual_ops.cu", "dli_depth_average", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x0), _ptr(hist), out.numel(), _ptr(weights), int(count), _ptr(y), out.numel(), DT_CODE[y.dtype] if y is not None else 0,
+             _stream()), "depth_average")
+
+
+MINGRU_CHUNK = 64  # rows of a sequence that one thread walks when a portion is cut into chunks
+
+
+def mingru_scan(out: torch.Tensor, p: torch.Tensor, bz: torch.Tensor, bx: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+                state_slot: torch.Tensor, max_len: int = 0) -> None:
+    """minGRU over any mix of prompt portions and single tokens.  p [n, 3 W] = z | x | g projections; per channel
+    z = sigmoid(pz + bz), u = px + bx, c = u + 1/2 where u >= 0 else sigmoid(u), S <- (1 - z) S + z c, out = S * silu(pg).
+    state [slots, W] float32 holds S per request; ``max_len``: the longest sequence's rows in this step (0: unknown, walk plainly)."""
+    _need(out, "out"), _need(p, "p", out.dtype), _need(bz, "bz", torch.float32), _need(bx, "bx", torch.float32), _need(state, "state", torch.float32)
+    n, W = out.shape
+    seqs = state_slot.numel()
+    if tuple(p.shape) != (n, 3 * W) or out.dtype not in DT_CODE or state.shape[1] != W or q_start.numel() != seqs + 1:
+        raise KernelError("mingru_scan: shapes or dtype do not agree")
+    scratch = None
+    if max_len > 4 * MINGRU_CHUNK:
+        cps = -(-max_len // MINGRU_CHUNK)
+        scratch = torch.empty((2 * n + (2 * cps + 1) * seqs) * W, dtype=torch.float32, device=out.device)
+    f = _fn("mingru.cu", "dli_mingru_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             c_int, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(p), _ptr(bz), _ptr(bx), _ptr(state), _ptr(q_start), _ptr(state_slot), n, seqs, W, int(max_len), MINGRU_CHUNK,
+             _ptr(scratch), DT_CODE[out.dtype], _stream()), "mingru_scan")
+
+
+def diff_prep(q_out: torch.Tensor, proj: torch.Tensor, k_col: int, v_col: int, wq: torch.Tensor, wk: torch.Tensor | None, eps: float,
+              positions: torch.Tensor, freq: torch.Tensor, amp: float, slots: torch.Tensor | None, k_pool: torch.Tensor | None,
+              v_pool: torch.Tensor | None, num_heads: int, num_kv_heads: int, dim: int, vdim: int, rot: int, page_size: int) -> None:
+    """Query and key preparation of differential attention.  proj rows hold q [heads][2 maps][dim] from column 0 and, when the
+    layer has keys and values of its own (k_col >= 0), k [kv_heads][2][dim] from k_col and v [kv_heads][vdim] from v_col.
+    Every map of every head is divided by its root mean square over dim (eps inside the root) and multiplied by wq (wk), then
+    its first ``rot`` dimensions are rotated in pairs (2i, 2i + 1) by the angle position * freq[i], cosine and sine times ``amp``.
+    q goes to q_out [n, heads * 2 * dim]; k and v go to the pages at ``slots`` (k_pool [pages, kv_heads, page_size, 2 dim],
+    v_pool [pages, kv_heads, page_size, vdim])."""
+    _need(q_out, "q_out"), _need(proj, "proj", q_out.dtype), _need(wq, "wq", torch.float32), _need(freq, "freq", torch.float32)
+    n = proj.shape[0]
+    writes = k_col >= 0
+    if q_out.dtype not in DT_CODE or tuple(q_out.shape) != (n, num_heads * 2 * dim) or rot % 2 or rot > dim or freq.numel() < rot // 2:
+        raise KernelError("diff_prep: shapes or dtype do not agree")
+    if writes:
+        _need(wk, "wk", torch.float32), _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", q_out.dtype), _need(v_pool, "v_pool", q_out.dtype)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, 2 * dim) or tuple(v_pool.shape[1:]) != (num_kv_heads, page_size, vdim):
+            raise KernelError("diff_prep: the pools' shapes do not agree with the heads")
+    f = _fn("diff_attention.cu", "dli_diff_prep", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float,
+                                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(q_out), _ptr(proj), proj.shape[1], int(k_col), int(v_col), _ptr(wq), _ptr(wk), float(eps), _ptr(positions), _ptr(freq), float(amp),
+             _ptr(slots if writes else None), _ptr(k_pool if writes else None), _ptr(v_pool if writes else None), n, num_heads, num_kv_heads, dim,
+             vdim, rot, page_size, DT_CODE[q_out.dtype], _stream()), "diff_prep")
+
+
+def diff_attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
+                        seq_of_token: torch.Tensor, positions: torch.Tensor, gate: torch.Tensor | None, num_heads: int, scale: float,
+                        window: int | None, keep_first: int, lam: float, post: float, eps: float) -> None:
+    """Differential attention on CUDA cores for every token of the step, both maps, the difference a1 - lam * a2, the head's
+    RMS norm (no weight) times ``post`` and the gate sigmoid(gate[t, head]) in one kernel.  q [n, heads * 2 * dim] (prepared),
+    out [n, heads * vdim]; ``gate`` [n, heads] may be a column slice of wider rows (or None).  Position i sees j <= i when
+    i - j < window or j < keep_first (window None: all)."""
+    _need(out, "out"), _need(q, "q", out.dtype), _need(k_pool, "k_pool", out.dtype), _need(v_pool, "v_pool", out.dtype)
+    n = q.shape[0]
+    _, nkv, page_size, d2 = k_pool.shape
+    vdim = v_pool.shape[3]
+    if out.dtype not in DT_CODE or d2 % 2 or tuple(q.shape) != (n, num_heads * d2) or tuple(out.shape) != (n, num_heads * vdim) or num_heads % nkv:
+        raise KernelError("diff_attention_simt: shapes or dtype do not agree")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != out.dtype or gate.shape != (n, num_heads) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("diff_attention_simt: gate must be [n, heads] with unit column stride")
+        gate_stride = gate.stride(0)
+    f = _fn("diff_attention.cu", "dli_diff_attention_simt", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                                             c_float, c_float, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1], _ptr(seq_of_token), _ptr(positions),
+             _ptr(gate), gate_stride, n, num_heads, nkv, d2 // 2, vdim, page_size, int(window or 0), int(keep_first), float(scale), float(lam),
+             float(post), float(eps), DT_CODE[out.dtype], _stream()), "diff_attention_simt")

@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..cache.needs import PagedKVNeed
@@ -256,4 +258,117 @@ class LatentAttention(Part):
         out = torch.empty((n, self.nh * self.dv), dtype=x.dtype, device=x.device)
         heads_product(latent.view(n, self.nh, self.row)[:, :, : self.rank], self.w_uv, out.view(n, self.nh, self.dv),
                       gate=proj[:, self.gate_col : self.gate_col + self.nh * self.dv] if self.gated else None)
+        return project(out, self.wo)
+
+
+def paired_rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> tuple[list[float], float]:
+    """Frequencies f_i = base^(-2i/dims), i < dims / 2, of a rotation that pairs dimension 2i with 2i + 1, and the factor on its
+    cosines and sines.  With ``scaling`` (factor, original, fast, slow) the YaRN correction: dimensions whose wavelength fits
+    the original context many times keep their frequency, those that turn less than ``slow`` times in it are divided by
+    ``factor``, with a linear ramp between, and cosine and sine are multiplied by 0.1 ln(factor) + 1."""
+    freq = [base ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return freq, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def turns_to_dim(turns: float) -> float:  # the (fractional) pair index whose wavelength fits the original context ``turns`` times
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(turns_to_dim(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(turns_to_dim(float(scaling["slow"]))), dims - 1)
+    out = []
+    for i, f in enumerate(freq):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f / factor * ramp + f * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
+@register_part("mixer", "diff_attention")
+class DiffAttention(Part):
+    """Differential attention: every query head carries two attention maps over the same values, combined by a difference.
+
+    q has heads x 2 x head_dim rows and k kv_heads x 2 x head_dim, head by head as [map 1 | map 2]; v has kv_heads x value_dim.
+    Every map of every head of q and k is RMS-normed over head_dim with a weight of that size (one for q, one for k) and then
+    rotated on its first ``rotary_dim`` dimensions, dimension 2i paired with 2i + 1 (``paired_rotary_frequencies``).  Causal,
+    with an optional sliding ``window`` that always keeps a sequence's first ``keep_first`` tokens.  With a1, a2 the two
+    maps' outputs of a head and lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (one number for the layer):
+
+        o = a1 - lambda a2;    o <- o / rms(o) * (1 - diff);    o <- o * sigmoid(W_g x)[head];    out = W_o [o of all heads]
+
+    A layer with ``own_kv`` false has no k and v tensors: its run step reads another step's cache (keys as that layer wrote
+    them, normed and rotated) with its own queries, mask and everything else.  A cached token is one key row of
+    2 head_dim numbers and one value row of value_dim numbers per KV head.  ``retain_window`` / ``retain_first`` say what the
+    cache has to keep (the widest window and most first tokens among the layers that read it).
+
+    One product yields q | k | v | g; one kernel norms, rotates and writes the cache; one kernel attends (both maps, the
+    difference, the head's norm and the gate).
+    params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, scale, window, keep_first, diff, eps, rotary_dim, theta,
+    rotary_scaling, own_kv, retain_window, retain_first, tensors (names of q, k, v, g, o, q_norm, k_norm, lq1, lk1, lq2, lk2)."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.d, self.dv = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"]), int(p["value_dim"])
+        self.scale, self.diff, self.eps = float(p["scale"]), float(p["diff"]), float(p["eps"])
+        self.window = int(p["window"]) if p.get("window") else None
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.own_kv = bool(p.get("own_kv", True))
+        self.retain_window = p.get("retain_window", self.window)
+        self.retain_first = int(p.get("retain_first", self.keep_first))
+        self.rot = int(p.get("rotary_dim") or 0)
+        if self.nh % self.nkv or self.rot % 2 or self.rot > self.d:
+            raise ValueError("diff_attention: num_heads must be a multiple of num_kv_heads, rotary_dim even and at most head_dim")
+        freq, self.amp = paired_rotary_frequencies(self.rot, float(p["theta"]), p.get("rotary_scaling")) if self.rot else ([0.0], 1.0)
+        self.freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(env.device)
+        defaults = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight", "o": "o_proj.weight",
+                    "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "lq1": "lambda_q1", "lk1": "lambda_k1", "lq2": "lambda_q2",
+                    "lk2": "lambda_k2"}
+        self.names = {role: tensor_name(spec, role, default) for role, default in defaults.items()}
+        self.q_cols = self.nh * 2 * self.d
+        self.k_col = self.q_cols if self.own_kv else -1
+        self.v_col = self.q_cols + self.nkv * 2 * self.d if self.own_kv else -1
+        self.g_col = self.q_cols + (self.nkv * (2 * self.d + self.dv) if self.own_kv else 0)
+        self.w_in = self.wo = self.wq_norm = self.wk_norm = None
+        self.lam = self.diff
+
+    def declare(self):
+        nm, H, d = self.names, self.hidden, self.d
+        out = {nm["q"]: TensorDecl((self.q_cols, H)), nm["g"]: TensorDecl((self.nh, H)), nm["o"]: TensorDecl((H, self.nh * self.dv)),
+               nm["q_norm"]: TensorDecl((d,), "vector32")}
+        out.update({nm[r]: TensorDecl((d,), "vector32") for r in ("lq1", "lk1", "lq2", "lk2")})
+        if self.own_kv:
+            out.update({nm["k"]: TensorDecl((self.nkv * 2 * d, H)), nm["v"]: TensorDecl((self.nkv * self.dv, H)),
+                        nm["k_norm"]: TensorDecl((d,), "vector32")})
+        return out
+
+    def load(self, tensors):
+        nm = self.names
+        rows = [tensors[nm["q"]]] + ([tensors[nm["k"]], tensors[nm["v"]]] if self.own_kv else []) + [tensors[nm["g"]]]
+        self.w_in = torch.cat(rows, 0).contiguous()
+        self.wo, self.wq_norm = tensors[nm["o"]], tensors[nm["q_norm"]]
+        self.wk_norm = tensors[nm["k_norm"]] if self.own_kv else None
+        l1 = (tensors[nm["lq1"]].double() * tensors[nm["lk1"]].double()).sum().item()
+        l2 = (tensors[nm["lq2"]].double() * tensors[nm["lk2"]].double()).sum().item()
+        self.lam = math.exp(l1) - math.exp(l2) + self.diff
+
+    def cache_need(self):
+        return PagedKVNeed(self.nkv, 2 * self.d, self.retain_window, value_dim=self.dv,
+                           keep_first=self.retain_first if self.retain_window is not None else 0)
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        n = x.shape[0]
+        if cache.writes != self.own_kv:
+            raise RuntimeError("diff_attention: a layer with keys and values of its own writes its cache, one without reads another's")
+        proj = project(x, self.w_in)  # q | k | v | g
+        group = batch.group(cache.group)
+        q = torch.empty((n, self.q_cols), dtype=x.dtype, device=x.device)
+        ops.diff_prep(q, proj, self.k_col, self.v_col, self.wq_norm, self.wk_norm, self.eps, batch.positions, self.freq, self.amp,
+                      group.slots if self.own_kv else None, cache.k if self.own_kv else None, cache.v if self.own_kv else None,
+                      self.nh, self.nkv, self.d, self.dv, self.rot, cache.page_size)
+        out = torch.empty((n, self.nh * self.dv), dtype=x.dtype, device=x.device)
+        attn_kernels.diff_attention(out, q, cache, batch, proj[:, self.g_col : self.g_col + self.nh], self.nh, self.scale, self.window,
+                                    self.keep_first, self.lam, 1.0 - self.diff, self.eps)
         return project(out, self.wo)

@@ -150,6 +150,17 @@ class ResidualStream:
     def __init__(self, h: torch.Tensor, pending=None) -> None:
         self.h = h
         self._pending = pending
+        # h once more in the activation dtype, when the kernel that last wrote h wrote that too (layers whose sublayers read
+        # the stream itself); whoever changes h sets it anew or to None
+        self.cast: torch.Tensor | None = None
+
+    def activation(self, dtype: torch.dtype) -> torch.Tensor:
+        """The stream as a sublayer's product reads it: h itself in float32, else h rounded to ``dtype``."""
+        if dtype == torch.float32:
+            return self.h
+        if self.cast is None or self.cast.dtype != dtype:
+            self.cast = self.h.to(dtype)
+        return self.cast
 
     @property
     def pending(self):

@@ -127,3 +127,49 @@ class ParallelBlock(Part):
             yf = normed_input(self.ffn_norm, stream.h, None, self.ffn) if self.has_ffn else None
         a = self.mixer.forward(ya, batch, cache)
         stream.pending = PendingSum(a, self.ffn.forward(yf) if self.has_ffn else None)
+
+
+@register_part("arrangement", "outnorm")
+class OutNormBlock(Part):
+    """x <- x + post_a(mixer(x)); x <- x + post_f(ffn(x)): the sublayers read the stream itself, and only their OUTPUT is normed
+    (by a norm with ``add_scaled_into``, which also carries the factor of the addition).  Roles: mixer, mixer_post_norm, and —
+    a layer may have no feed-forward — ffn, ffn_post_norm; then, optionally, ``after_1`` and ``after_2``: stream_entry parts
+    that act on the stream behind the sublayers, in that order (a part with ``begin(stream, batch)`` is also told when the
+    layer starts).  In a 16-bit dtype the kernel that adds to the float32 stream also writes it in that dtype, which is what
+    the next product reads; nothing else is rounded."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env: BuildEnv) -> None:
+        self.spec, self.env = spec, env
+        self.mixer = build_part("mixer", spec.parts["mixer"], env)
+        self.mixer_post_norm = build_part("norm", spec.parts["mixer_post_norm"], env)
+        self.has_ffn = "ffn" in spec.parts
+        if self.has_ffn:
+            self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
+            self.ffn_post_norm = build_part("norm", spec.parts["ffn_post_norm"], env)
+        self.after = [build_part("stream_entry", spec.parts[role], env) for role in ("after_1", "after_2") if role in spec.parts]
+        for norm in (self.mixer_post_norm, *([self.ffn_post_norm] if self.has_ffn else [])):
+            if not hasattr(norm, "add_scaled_into"):
+                raise ValueError("outnorm: the norm behind a sublayer must offer add_scaled_into(h, a, want_cast)")
+
+    def children(self):
+        return [self.mixer, self.mixer_post_norm] + ([self.ffn, self.ffn_post_norm] if self.has_ffn else []) + self.after
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        for part in self.after:
+            begin = getattr(part, "begin", None)
+            if begin is not None:
+                begin(stream, batch)
+        h = stream.settle()
+        dtype = self.env.dtype
+        a = self.mixer.forward(stream.activation(dtype), batch, cache)
+        stream.cast = self.mixer_post_norm.add_scaled_into(h, a, want_cast=self.has_ffn or bool(self.after))
+        if self.has_ffn:
+            f = self.ffn.forward(stream.activation(dtype))
+            stream.cast = self.ffn_post_norm.add_scaled_into(h, f, want_cast=bool(self.after))
+        for i, part in enumerate(self.after):
+            part.apply(stream, batch, want_cast=True)

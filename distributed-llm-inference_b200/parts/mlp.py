@@ -17,7 +17,9 @@ class SwiGLU(Part):
     ``ops.GLU_ACTIVATIONS``.  gate and up are read by their own names and laid together at load, so one
     product yields both: side by side, or — when the intermediate size is a multiple of 64 — interleaved in
     blocks of 64 rows, the layout in which the decode product applies act(gate) * up in its own epilogue.
-    params: hidden_size, intermediate_size, activation (default ``silu``), tensors (names of gate, up, down)."""
+    With ``limit`` > 0 the gate is bounded from above by it and up to [-limit, limit] before the activation, and ``up_shift`` is
+    added to up: act(min(gate, limit)) * (clamp(up) + up_shift).
+    params: hidden_size, intermediate_size, activation (default ``silu``), limit, up_shift, tensors (names of gate, up, down)."""
 
     graph_capturable = True
     takes_scaled_rows = True  # the input only goes to the gate | up product
@@ -30,6 +32,9 @@ class SwiGLU(Part):
         self.activation = spec.params.get("activation", "silu")
         if self.activation not in ops.GLU_ACTIVATIONS:
             raise ValueError(f"activation {self.activation!r} is not supported (known: {sorted(ops.GLU_ACTIVATIONS)})")
+        self.limit = float(spec.params.get("limit") or 0.0)
+        self.up_shift = float(spec.params.get("up_shift") or 0.0)
+        self.plain_glu = self.limit == 0.0 and self.up_shift == 0.0 and self.activation in ("silu", "gelu_tanh")  # what the products' epilogues take
         self.names = {role: tensor_name(spec, role, role + "_proj.weight") for role in ("gate", "up", "down")}
         self.w_gate_up: torch.Tensor | None = None
         self.tiled = False
@@ -54,14 +59,14 @@ class SwiGLU(Part):
         self.w_down = tensors[self.names["down"]]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.tiled and fused_epilogue(x):
+        if self.tiled and self.plain_glu and fused_epilogue(x):
             act = ops.skinny_gemm_swiglu(x, self.w_gate_up, self.activation)
-        elif self.tiled and dense_product(x, 2 * self.inter, "swiglu"):
+        elif self.tiled and self.plain_glu and dense_product(x, 2 * self.inter, "swiglu"):
             act = ops.dense_gemm_swiglu(x, self.w_gate_up, self.activation)
         else:
             gate_up = project(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-            ops.silu_mul(act, gate_up, self.tiled, self.activation)
+            ops.silu_mul(act, gate_up, self.tiled, self.activation, self.limit, self.up_shift)
         return last_product(act, self.w_down, self.defer_output)
 
 

@@ -35,6 +35,63 @@ class TokenEmbedding(Part):
         return h
 
 
+@register_part("embedding", "pair_hash_embedding")
+class PairHashEmbedding(Part):
+    """h = table[token] * scale + pair_table[row]: beside the token's own row, a row of a second table chosen by a hash of
+    the token and the one in front of it, row = (previous * mul_prev + token * mul_cur) mod buckets; a sequence's first
+    token takes the table's last row (number ``buckets``).  The token in front of a step's first one is part of the
+    request's state: one int32 per state slot, which the kernel reads and then leaves the step's last token in.
+    Without ``pair`` it is a scaled embedding.  params: vocab_size, hidden_size, tensor, scale, pair (tensor, buckets,
+    mul_prev, mul_cur; or None)."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.vocab, self.hidden = int(p["vocab_size"]), int(p["hidden_size"])
+        self.scale = float(p.get("scale", 1.0))
+        self.name = tensor_name(spec, "weight", "weight")
+        self.pair = p.get("pair")
+        if self.pair is not None:
+            self.buckets, self.mul_prev, self.mul_cur = int(self.pair["buckets"]), int(self.pair["mul_prev"]), int(self.pair["mul_cur"])
+            if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
+                raise ValueError("pair_hash_embedding: buckets must be positive and the multipliers not negative")
+        self.weight = self.pair_table = None
+
+    def declare(self):
+        out = {self.name: TensorDecl((self.vocab, self.hidden))}
+        if self.pair is not None:
+            out[self.pair["tensor"]] = TensorDecl((self.buckets + 1, self.hidden))
+        return out
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+        if self.pair is not None:
+            self.pair_table = tensors[self.pair["tensor"]]
+
+    def cache_need(self):
+        from ..cache.needs import StateNeed
+
+        return StateNeed((1,), torch.int32) if self.pair is not None else None
+
+    def forward_step(self, batch, cache) -> ResidualStream:
+        n = batch.token_ids.numel()
+        h = torch.empty((n, self.hidden), dtype=torch.float32, device=batch.token_ids.device)
+        y = torch.empty((n, self.hidden), dtype=self.env.dtype, device=h.device) if self.env.dtype != torch.float32 else None
+        if self.pair is None:
+            ops.pair_embedding(h, self.weight, self.scale, None, 0, 0, 0, batch.token_ids, batch.positions, batch.seq_of_token, batch.q_start,
+                               batch.state_slot, None, y)
+        else:
+            if cache is None or cache.state is None:
+                raise RuntimeError("pair_hash_embedding: the step brought no state slots for the previous token")
+            ops.pair_embedding(h, self.weight, self.scale, self.pair_table, self.buckets, self.mul_prev, self.mul_cur, batch.token_ids,
+                               batch.positions, batch.seq_of_token, batch.q_start, batch.state_slot, cache.state, y)
+        stream = ResidualStream(h)
+        stream.cast = y
+        return stream
+
+
 @register_part("head", "lm_head")
 class LMHead(Part):
     """logits = y W^T in float32, W the embedding matrix when ``tied_to`` names it
@@ -146,10 +203,20 @@ class DecoderModel:
             needs.append(ask() if ask is not None and step.cache_of is None else None)
         return needs
 
+    def embedding_need(self):
+        """What the embedding keeps per request between steps (StateNeeds, or None): an embedding that reads the token in
+        front of a step's first one, for instance."""
+        ask = getattr(self.embedding, "cache_need", None)
+        return ask() if ask is not None else None
+
     def forward(self, batch, caches) -> torch.Tensor:
         """Logits [k, vocab] (float32) at ``batch.logit_rows``; every token's cache entries are written."""
         batch.scratch.clear()
-        stream = ResidualStream(self.embedding.forward(batch.token_ids))
+        embed_step = getattr(self.embedding, "forward_step", None)  # an embedding that reads more of the step than its token ids
+        if embed_step is not None:
+            stream = embed_step(batch, getattr(caches, "embedding", None))
+        else:
+            stream = ResidualStream(self.embedding.forward(batch.token_ids))
         for i, step in enumerate(self.spec.run_order):
             if step.entry is not None:
                 self.entries[step.entry].apply(stream, batch)

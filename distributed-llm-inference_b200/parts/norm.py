@@ -112,3 +112,48 @@ class LayerNorm(Part):
 
     def add_into(self, h: torch.Tensor, a: torch.Tensor) -> None:
         ops.post_add_layernorm(None, h, a, self.weight, None, self.eps, 0.0)
+
+
+@register_part("norm", "group_rmsnorm")
+class GroupRMSNorm(Part):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive parts, each is divided by its own
+    sqrt(mean(part^2) + eps), and the whole is multiplied by a weight; float32 arithmetic, one rounding.  groups = 1 is the
+    plain RMS norm.  Two uses: ``add_norm`` norms rows of the stream (a model's last norm), and ``add_scaled_into(h, a)`` is
+    h += mult * norm(a) * weight, for layers that norm a sublayer's OUTPUT before the residual addition.
+    params: size, eps, groups (default 1), mult (default 1), tensor (the weight's name; default prefix + "weight")."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.groups = int(spec.params.get("groups", 1))
+        self.mult = float(spec.params.get("mult", 1.0))
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"group_rmsnorm: size={self.size} is not a multiple of groups={self.groups}")
+        self.name = tensor_name(spec, "weight", "weight")
+        self.weight: torch.Tensor | None = None
+
+    def declare(self):
+        return {self.name: TensorDecl((self.size,), "vector32")}
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+
+    def add_norm(self, h: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor:
+        if delta is not None:
+            if rows is not None:
+                raise ValueError("group_rmsnorm: a plain delta is added to the whole stream (rows=None)")
+            h += delta.float()
+        n = h.shape[0] if rows is None else rows.numel()
+        y = torch.empty((n, self.size), dtype=self.env.dtype, device=h.device)
+        ops.group_norm_rows(y, h, self.weight, self.groups, self.eps, rows)
+        return y
+
+    def add_scaled_into(self, h: torch.Tensor, a: torch.Tensor, want_cast: bool = False) -> torch.Tensor | None:
+        """h += mult * norm(a) * weight.  With ``want_cast`` (and a in a 16-bit dtype) the new h is also returned in a's dtype,
+        written by the same kernel: what the next sublayer's product reads."""
+        y = torch.empty_like(a) if want_cast and a.dtype != torch.float32 else None
+        ops.group_norm_add(h, a, self.weight, self.groups, self.eps, self.mult, y)
+        return y

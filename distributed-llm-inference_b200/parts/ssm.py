@@ -173,3 +173,46 @@ class GatedDeltaRule(Part):
         gated = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         ops.gated_group_rmsnorm(gated, o, u, self.g_col, w["norm"], self.heads, self.eps, gate_after=True)
         return project(gated, w["o"])
+
+
+@register_part("mixer", "mingru")
+class MinGRU(Part):
+    """minGRU on any mix of prompt portions and decoded tokens: a gated recurrence whose gates read only the current token.
+
+    One product yields z | x | g (``width`` columns each).  With z = sigmoid(z + b_z), u = x + b_x and the candidate
+    c = u + 1/2 where u >= 0, sigmoid(u) elsewhere, element by element
+
+        S_t = (1 - z_t) S_(t-1) + z_t c_t,        out_t = W_o (S_t * silu(g_t)).
+
+    A request keeps S (float32, ``width`` numbers) in its state slot; it starts at zero.  Gates, candidate and state are float32.
+    params: hidden_size, width, tensors (names of z, z_bias, x, x_bias, g, o)."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden, self.width = int(p["hidden_size"]), int(p["width"])
+        defaults = {"z": "z_proj.weight", "z_bias": "z_proj.bias", "x": "x_proj.weight", "x_bias": "x_proj.bias", "g": "g_proj.weight",
+                    "o": "o_proj.weight"}
+        self.names = {role: tensor_name(spec, role, default) for role, default in defaults.items()}
+        self.w_in = self.wo = self.bz = self.bx = None
+
+    def declare(self):
+        nm, H, W = self.names, self.hidden, self.width
+        return {nm["z"]: TensorDecl((W, H)), nm["x"]: TensorDecl((W, H)), nm["g"]: TensorDecl((W, H)), nm["o"]: TensorDecl((H, W)),
+                nm["z_bias"]: TensorDecl((W,), "vector32"), nm["x_bias"]: TensorDecl((W,), "vector32")}
+
+    def load(self, tensors):
+        nm = self.names
+        self.w_in = torch.cat([tensors[nm["z"]], tensors[nm["x"]], tensors[nm["g"]]], 0).contiguous()
+        self.wo, self.bz, self.bx = tensors[nm["o"]], tensors[nm["z_bias"]], tensors[nm["x_bias"]]
+
+    def cache_need(self):
+        return StateNeed((self.width,), torch.float32)
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        p = project(x, self.w_in)  # z | x | g
+        gated = torch.empty((x.shape[0], self.width), dtype=x.dtype, device=x.device)
+        ops.mingru_scan(gated, p, self.bz, self.bx, cache.state, batch.q_start, batch.state_slot, max_len=batch.max_q_len)
+        return project(gated, self.wo)

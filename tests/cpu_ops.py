@@ -71,16 +71,18 @@ def _gelu_tanh(z):
     return 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z**3)))
 
 
-def silu_mul(out, gate_up, tiled=False, activation="silu"):
+def silu_mul(out, gate_up, tiled=False, activation="silu", limit=0.0, up_shift=0.0):
     n, inter = out.shape
     if tiled:
         blocks = gate_up.view(n, inter // 64, 2, 64)
         gate, up = blocks[:, :, 0].reshape(n, inter), blocks[:, :, 1].reshape(n, inter)
     else:
         gate, up = gate_up[:, :inter], gate_up[:, inter:]
-    g = gate.float()
-    act = g / (1 + torch.exp(-g)) if activation == "silu" else _gelu_tanh(g)
-    out.copy_((act * up.float()).to(out.dtype))
+    g, u = gate.float(), up.float()
+    if limit > 0:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    act = {"silu": lambda: g / (1 + torch.exp(-g)), "gelu_tanh": lambda: _gelu_tanh(g), "quick_gelu": lambda: g / (1 + torch.exp(-1.702 * g))}[activation]()
+    out.copy_((act * (u + up_shift)).to(out.dtype))
 
 
 def add_rmsnorm_pair(y1, y2, h, a, b, w1, w2, eps, rows=None):
@@ -462,6 +464,115 @@ class CpuSampler:
         return CpuPending(self._run(logits, params, seeds, draws))
 
 
+
+def pair_embedding(h, table, scale, pair_table, buckets, mul_prev, mul_cur, ids, positions, seq_of_token, q_start, state_slot, prev_state, y=None):
+    idl = ids.long()
+    x = table[idl].float() * scale
+    if pair_table is not None:
+        first = q_start.long()[seq_of_token.long()]
+        at = torch.arange(ids.numel())
+        prev_state = prev_state.view(-1)
+        prev = torch.where(at > first, idl[(at - 1).clamp(min=0)], prev_state[state_slot.long()[seq_of_token.long()]].long())
+        rows = (prev * mul_prev + idl * mul_cur) % buckets
+        rows = torch.where(positions == 0, torch.full_like(rows, buckets), rows)
+        x = x + pair_table[rows].float()
+        for s in range(state_slot.numel()):
+            if q_start[s + 1] > q_start[s]:
+                prev_state[state_slot[s].long()] = ids[q_start[s + 1].long() - 1]
+    h.copy_(x)
+    if y is not None:
+        y.copy_(x.to(y.dtype))
+
+
+def _group_unit(x, groups, eps):
+    n, H = x.shape
+    parts = x.view(n, groups, H // groups)
+    return (parts * torch.rsqrt((parts * parts).mean(-1, keepdim=True) + eps)).reshape(n, H)
+
+
+def group_norm_add(h, a, weight, groups, eps, mult, y=None):
+    h += mult * (_group_unit(a.float(), groups, eps) * weight)
+    if y is not None:
+        y.copy_(h.to(y.dtype))
+
+
+def group_norm_rows(y, h, weight, groups, eps, rows=None):
+    x = h if rows is None else h[rows.long()]
+    y.copy_((_group_unit(x, groups, eps) * weight).to(y.dtype))
+
+
+def gelu_mul_rows(g, table, col0, ids):
+    e = table[ids.long(), col0 : col0 + g.shape[1]].float()
+    g.copy_((_gelu_tanh(g.float()) * e).to(g.dtype))
+
+
+def depth_average(out, x0, hist, weights, count, y=None):
+    out.copy_(weights[0] * x0 + (hist[: count - 1] * weights[1:count, None, None]).sum(0))
+    if y is not None:
+        y.copy_(out.to(y.dtype))
+
+
+def mingru_scan(out, p, bz, bx, state, q_start, state_slot, max_len=0):
+    W = out.shape[1]
+    pf = p.float()
+    z = torch.sigmoid(pf[:, :W] + bz)
+    u = pf[:, W : 2 * W] + bx
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    g = pf[:, 2 * W :]
+    for s in range(state_slot.numel()):
+        slot = int(state_slot[s])
+        S = state[slot].clone()
+        for r in range(int(q_start[s]), int(q_start[s + 1])):
+            S = (1 - z[r]) * S + z[r] * cand[r]
+            out[r] = (S * g[r] * torch.sigmoid(g[r])).to(out.dtype)
+        state[slot] = S
+
+
+def diff_prep(q_out, proj, k_col, v_col, wq, wk, eps, positions, freq, amp, slots, k_pool, v_pool, num_heads, num_kv_heads, dim, vdim, rot, page_size):
+    n = proj.shape[0]
+    ang = positions.float()[:, None] * freq[None, : rot // 2]
+    cos, sin = (ang.cos() * amp)[:, None, :], (ang.sin() * amp)[:, None, :]
+
+    def prepare(x, w):  # x [n, units, dim]
+        x = x.float()
+        x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+        a, b = x[..., 0:rot:2].clone(), x[..., 1:rot:2].clone()
+        x[..., 0:rot:2] = a * cos - b * sin
+        x[..., 1:rot:2] = b * cos + a * sin
+        return x
+
+    q_out.copy_(prepare(proj[:, : num_heads * 2 * dim].reshape(n, num_heads * 2, dim), wq).reshape(n, -1).to(q_out.dtype))
+    if k_col >= 0:
+        k = prepare(proj[:, k_col : k_col + num_kv_heads * 2 * dim].reshape(n, num_kv_heads * 2, dim), wk).reshape(n, num_kv_heads, 2 * dim)
+        page, off = (slots // page_size).long(), (slots % page_size).long()
+        k_pool[page, :, off, :] = k.to(k_pool.dtype)
+        v_pool[page, :, off, :] = proj[:, v_col : v_col + num_kv_heads * vdim].reshape(n, num_kv_heads, vdim)
+
+
+def diff_attention_simt(out, q, k_pool, v_pool, block_tables, seq_of_token, positions, gate, num_heads, scale, window, keep_first, lam, post, eps):
+    n = q.shape[0]
+    _, nkv, page_size, d2 = k_pool.shape
+    dim, vdim = d2 // 2, v_pool.shape[3]
+    qf = q.float().view(n, num_heads, 2, dim)
+    for t in range(n):
+        p = int(positions[t])
+        table = block_tables[int(seq_of_token[t])].long()
+        keys = torch.arange(p + 1)
+        if window:
+            keys = keys[(p - keys < window) | (keys < keep_first)]
+        page, off = table[keys // page_size], keys % page_size
+        for h in range(num_heads):
+            g = h // (num_heads // nkv)
+            k = k_pool[page, g, off].float().view(-1, 2, dim)
+            v = v_pool[page, g, off].float()
+            a = [torch.softmax((k[:, m] @ qf[t, h, m]) * scale, 0) @ v for m in range(2)]
+            o = a[0] - lam * a[1]
+            o = o * torch.rsqrt((o * o).mean() + eps) * post
+            if gate is not None:
+                o = o * torch.sigmoid(gate[t, h].float())
+            out[t, h * vdim : (h + 1) * vdim] = o.to(out.dtype)
+
+
 OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_page, "add_rmsnorm": add_rmsnorm,
        "rotary_table": rotary_table, "rotary_store": rotary_store, "silu_mul": silu_mul, "paged_attention_simt": paged_attention_simt,
        "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
@@ -472,7 +583,9 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "qk_norm_rotary_store": qk_norm_rotary_store, "sigmoid_gate": sigmoid_gate, "causal_conv_silu": causal_conv_silu,
        "conv_state_update": conv_state_update, "ssm_scan": ssm_scan, "gated_group_rmsnorm": gated_group_rmsnorm,
        "add_rmsnorm_pair": add_rmsnorm_pair, "scale_softcap": scale_softcap, "latent_prep": latent_prep, "delta_rule_scan": delta_rule_scan,
-       "heads_matvec": heads_matvec, "heads_matvec_supported": lambda in_features, features: True}
+       "heads_matvec": heads_matvec, "heads_matvec_supported": lambda in_features, features: True,
+       "pair_embedding": pair_embedding, "group_norm_add": group_norm_add, "group_norm_rows": group_norm_rows, "gelu_mul_rows": gelu_mul_rows,
+       "depth_average": depth_average, "mingru_scan": mingru_scan, "diff_prep": diff_prep, "diff_attention_simt": diff_attention_simt}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered
