@@ -687,6 +687,161 @@ def sugonex_kernels(size, pk, tokens=4096, seqs=64):
     return out
 
 
+def pokadra_sizes(width, heads, kv_heads, dim, window, gru, ff, pz, vocab=32000):
+    """A Pokadra model of eight layers (differential attention, minGRU, differential attention, minGRU, differential
+    attention on the third layer's keys and values, minGRU, differential attention, minGRU) and the Pazenex configuration
+    of the same width, feed-forward size, number of layer runs and window (``pz``: its attention and state-space sizes:
+    twice the heads of half the size, since a differential head is two maps of ``dim`` over values of 2 ``dim``)."""
+    def mlp():
+        return {"kind": "dense", "ff": ff, "limit": 7.0}
+
+    def att(kv_from=None):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": 2 * dim, "scale": dim**-0.5, "diff": 0.8,
+             "mask": {"size": window, "keep_first": 4},
+             "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mlp": mlp(), "mixer": m}
+
+    def rec():
+        return {"type": "mingru", "mlp": mlp(), "mixer": {"width": gru}}
+
+    pk = {"architecture": "Pokadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4}, "residual_mult": 0.5,
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "token_side": {"dim": 64},
+          "layers": [att(), rec(), att(), rec(), att(kv_from=2), rec(), att(), rec()]}
+    pazenex, _ = pazenex_sizes(width=width, heads=2 * heads, kv_heads=2 * kv_heads, dim=dim, ff=ff, vocab=vocab, **pz)
+    for layer in pazenex["layers"]:
+        if layer["type"] == "attention":
+            layer["mixer"]["window"] = window
+    return pk, pazenex
+
+
+# a differential head of two maps of ``dim`` over values of 2 ``dim`` stands where two ordinary heads of ``dim`` stood;
+# the minGRU is as wide as the Mamba-2 layer's inner size
+POKADRA_SIZES = {
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=64, window=1024, gru=2048, ff=4096, pz=dict(ssm_heads=32, state=64, groups=4)),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=64, window=1024, gru=4096, ff=8192, pz=dict(ssm_heads=64, state=128, groups=8)),
+    "w4096": dict(width=4096, heads=16, kv_heads=4, dim=128, window=1024, gru=8192, ff=14336, pz=dict(ssm_heads=128, state=128, groups=8)),
+}
+
+
+def pokadra_kernels(size, pk, tokens=4096, seqs=64):
+    """Every kernel of the Pokadra parts beside the like kernel of the Pazenex parts, at one size: a prompt portion of
+    ``tokens`` tokens and a decode step of ``seqs`` sequences at a context of 2,048 (both under the window of the size).  us,
+    the bytes (or operations) the kernel has to move, and the share of the measured HBM peak (of the measured bf16 rate for
+    attention over a portion)."""
+    import torch
+
+    from dli_b200.cache.pools import LayerCache
+    from dli_b200.engine.batch import GroupView, StepBatch
+    from dli_b200.kernels import attention as attn
+    from dli_b200.kernels import ops
+
+    dev, bf = "cuda", torch.bfloat16
+    W, nh, nkv, d, ff, window, gru = size["width"], size["heads"], size["kv_heads"], size["dim"], size["ff"], size["window"], size["gru"]
+    dv, page, side, vocab = 2 * d, 16, 64, 32000
+    pz = size["pz"]
+    out = {}
+
+    def record(name, us, nbytes, like=None, flops=None):
+        rec = {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops is not None:
+            rec["tflops_bf16"] = round(flops / us / 1e6, 1)
+            rec["bf16_frac"] = round(flops / us / 1e6 / pk["bf16_tflops"], 3)
+        if like:
+            rec["like"] = like
+        out[name] = rec
+
+    for label, n, S in (("portion", tokens, 1), ("decode", seqs, seqs)):
+        q_len = n // S
+        context = tokens if S == 1 else 2048
+        width = -(-context // page)
+        tables = torch.arange(S * width, dtype=torch.int32, device=dev).view(S, width)
+        q_start = torch.arange(S + 1, dtype=torch.int32, device=dev) * q_len
+        kv_len = torch.full((S,), context, dtype=torch.int32, device=dev)
+        seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), q_len).to(dev)
+        positions = (torch.arange(n, dtype=torch.int32) % q_len + (context - q_len)).to(dev)
+        slots = (seq_of * width * page + positions).to(torch.int32)
+        slot = torch.arange(S, dtype=torch.int32, device=dev)
+        batch = StepBatch(n=n, num_seqs=S, num_single=S if q_len == 1 else 0, token_ids=positions, positions=positions, seq_of_token=seq_of,
+                          q_start=q_start, kv_len=kv_len, state_slot=slot, logit_rows=positions[:0], groups=[GroupView(tables, slots)],
+                          q_lens=[q_len] * S, starts=[context - q_len] * S, state_slots=list(range(S)), max_q_len=q_len, max_kv_len=context,
+                          max_kv_len_single=context if q_len == 1 else 0)
+        pages = S * width
+        ids = torch.randint(0, vocab, (n,), dtype=torch.int32, device=dev)
+        h = torch.randn(n, W, device=dev)
+        a = torch.randn(n, W, device=dev).to(bf)
+        w1, w2 = torch.ones(W, device=dev), torch.ones(W, device=dev)
+        y = torch.empty(n, W, dtype=bf, device=dev)
+        # embedding with the hashed pair table
+        table, pair = torch.randn(vocab, W, device=dev).to(bf), torch.randn(65522, W, device=dev).to(bf)
+        prev = torch.zeros(S, dtype=torch.int32, device=dev)
+        record(f"{label}.pair_embedding", time_kernel(lambda: ops.pair_embedding(h, table, 1.0, pair, 65521, 31, 17, ids, positions, seq_of, q_start, slot, prev, y)),
+               n * W * 10, "embedding")
+        record(f"{label}.embedding", time_kernel(lambda: ops.embedding(h, table, ids)), n * W * 6)
+        # the norm behind a sublayer, added to the stream
+        record(f"{label}.group_norm_add", time_kernel(lambda: ops.group_norm_add(h, a, w1, 4, 1e-6, 0.5, y)), n * W * 12, "post_add_layernorm")
+        record(f"{label}.post_add_layernorm", time_kernel(lambda: ops.post_add_layernorm(y, h, a, w1, w2, 1e-6, 1e-6)), n * W * 12)
+        # the token's own input: gate * table row
+        g = torch.randn(n, side, device=dev).to(bf)
+        side_table = torch.randn(vocab, 8 * side, device=dev).to(bf)
+        record(f"{label}.gelu_mul_rows", time_kernel(lambda: ops.gelu_mul_rows(g, side_table, 3 * side, ids)), n * side * 6)
+        # the mixture of the layers' results (the fifth layer's: six streams in, one out and its bfloat16 copy)
+        hist = torch.randn(8, n, W, device=dev)
+        dw = torch.full((9,), 0.2, device=dev)
+        record(f"{label}.depth_average", time_kernel(lambda: ops.depth_average(hist[5], h, hist, dw, 6, y)), n * W * (6 * 4 + 4 + 2), "add_rmsnorm")
+        record(f"{label}.add_rmsnorm", time_kernel(lambda: ops.add_rmsnorm(y, h, a, w1, 1e-6)), n * W * 12)
+        # differential attention: preparation and attention, beside Pazenex's at twice the heads of half the size
+        kp = torch.randn(pages + 1, nkv, page, 2 * d, device=dev).to(bf)
+        vp = torch.randn(pages + 1, nkv, page, dv, device=dev).to(bf)
+        cols = nh * 2 * d + nkv * (2 * d + dv) + nh
+        proj = torch.randn(n, cols, device=dev).to(bf)
+        q = torch.empty(n, nh * 2 * d, dtype=bf, device=dev)
+        wn = torch.ones(d, device=dev)
+        freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2).float() / d))).to(dev)
+        moved = n * ((nh * 2 * d + nkv * (2 * d + dv)) * 4)
+        record(f"{label}.diff_prep", time_kernel(lambda: ops.diff_prep(q, proj, nh * 2 * d, nh * 2 * d + nkv * 2 * d, wn, wn, 1e-6, positions, freq, 1.2, slots,
+                                                                        kp, vp, nh, nkv, d, dv, d, page)), moved, "qk_norm_rotary_store")
+        ph, pkv = 2 * nh, 2 * nkv
+        kp2, vp2 = (torch.randn(pages + 1, pkv, page, d, device=dev).to(bf) for _ in range(2))
+        proj2 = torch.randn(n, (ph + 2 * pkv) * d, device=dev).to(bf)
+        wq2, wk2 = torch.ones(ph * d, device=dev), torch.ones(pkv * d, device=dev)
+        record(f"{label}.qk_norm_rotary_store", time_kernel(lambda: ops.qk_norm_rotary_store(proj2, wq2, wk2, 1e-6, positions, freq, slots, kp2, vp2, ph, pkv, d, d, page,
+                                                                                              values_from_keys=False)),
+               n * (ph + 2 * pkv) * d * 4)
+        att = torch.empty(n, nh * dv, dtype=bf, device=dev)
+        gate = proj[:, cols - nh :]
+        seen = sum(min(p + 1, window + 4) for p in range(context)) if S == 1 else float(min(context, window + 4))  # keys a token attends to
+        kv_read = S * min(context, window + 4 + (q_len if S == 1 else 0)) * nkv * (2 * d + dv) * 2
+        us = time_kernel(lambda: attn.diff_attention(att, q, LayerCache(0, kp, vp, page), batch, gate, nh, d**-0.5, window, 4, 0.5, 0.2, 1e-6))
+        record(f"{label}.diff_attention", us, kv_read + n * nh * (2 * d + dv) * 2, "sink_attention", flops=S * seen * nh * (4.0 * d + 4.0 * dv))
+        pq, po = torch.randn(n, ph * d, device=dev).to(bf), torch.empty(n, ph * d, dtype=bf, device=dev)
+        us = time_kernel(lambda: attn.paged_attention(po, pq, LayerCache(0, kp2, vp2, page), batch, ph, d**-0.5, window, sink=0.0))
+        record(f"{label}.sink_attention", us, kv_read + n * ph * d * 4, flops=S * seen * ph * 4.0 * d)
+        # the gate | up activation where it is a kernel of its own (9 to 511 tokens; otherwise it rides in the product's epilogue)
+        gu = torch.randn(n, 2 * ff, device=dev).to(bf)
+        act = torch.empty(n, ff, dtype=bf, device=dev)
+        record(f"{label}.quick_gelu_bounded_mul", time_kernel(lambda: ops.silu_mul(act, gu, True, "quick_gelu", 7.0, 1.0)), n * ff * 6, "silu_mul")
+        record(f"{label}.silu_mul", time_kernel(lambda: ops.silu_mul(act, gu, True)), n * ff * 6)
+        # minGRU beside the Mamba-2 scan of the Pazenex model of this size
+        p3 = torch.randn(n, 3 * gru, device=dev).to(bf)
+        gs = torch.empty(n, gru, dtype=bf, device=dev)
+        bz = torch.zeros(gru, device=dev)
+        state = torch.zeros(S, gru, device=dev)
+        us = time_kernel(lambda: ops.mingru_scan(gs, p3, bz, bz, state, q_start, slot, max_len=q_len))
+        record(f"{label}.mingru_scan", us, n * gru * 8 + S * gru * 8, "ssm_scan")
+        Hs, P, N, G = pz["ssm_heads"], 64, pz["state"], pz["groups"]
+        sin, sC = Hs * P, Hs * P + 2 * G * N
+        su = torch.randn(n, sin + sC + Hs, device=dev).to(bf)
+        xbc = torch.randn(n, sC, device=dev).to(bf)
+        sstate = torch.zeros(S, Hs, P, N, device=dev)
+        ys = torch.empty(n, sin, device=dev)
+        z3 = torch.zeros(Hs, device=dev)
+        us = time_kernel(lambda: ops.ssm_scan(ys, xbc, su, sin + sC, z3, z3, z3 + 1, sstate, q_start, slot, G, max_len=q_len))
+        record(f"{label}.ssm_scan", us, S * Hs * N * P * 8 + n * (sC * 2 + sin * 4))
+    return out
+
+
 SIMT_FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12  # CUDA-core multiply-adds of a B200 at 1.9 GHz: the scan's ceiling (no float32 tensor-core path)
 
 
@@ -694,6 +849,7 @@ DESIGNS = {
     # design -> (sizes by name, what builds the two configurations of a size, the closest existing model, the kernels' table)
     "pazenex": (DESIGN_SIZES, pazenex_sizes, "llama", design_kernels),
     "sugonex": (SUGONEX_SIZES, sugonex_sizes, "pazenex", sugonex_kernels),
+    "pokadra": (POKADRA_SIZES, pokadra_sizes, "pazenex", pokadra_kernels),
 }
 
 
@@ -935,7 +1091,7 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "sample"],
                     help="profiling runs: only the device-timed decode steps, only the prefill step, or only the sampling kernel (prints a short line)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the step's kernels one by one")
-    ap.add_argument("--design", default=None, choices=["pazenex", "sugonex"],
+    ap.add_argument("--design", default=None, choices=["pazenex", "sugonex", "pokadra"],
                     help="another measurement: this architecture beside Llama at equal sizes, and its kernels beside their likes (prints its own line)")
     ap.add_argument("--size", default=None, choices=list(DESIGN_SIZES), help="--design: one size only (every design has these names)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,

@@ -34,6 +34,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include <math_constants.h>
 
 using namespace dli;
 
@@ -110,7 +111,8 @@ struct DenseParams {
   __nv_bfloat16* v_pool;
   int nh, nkv, d, rot, page_size, write_kv;
   int act;        // EP_STORE: an activation on the (bfloat16-rounded) sums before they are stored: 0 none, 1 relu^2, 2 gelu-tanh, 3 silu
-                  // EP_SWIGLU: what is applied to the gate: 0 silu, 1 gelu-tanh
+                  // EP_SWIGLU: what is applied to the gate: 0 silu, 1 gelu-tanh, 2 g * sigmoid(1.702 g)
+  float glu_limit, glu_shift;  // EP_SWIGLU: act(min(gate, limit)) * (clamp(up, -limit, limit) + shift); limit 0: no bounds
   int skip_tile;  // -1 in every launch of the engine: the k step whose copies a test leaves out (dli_dense_gemm_wait_test)
 };
 
@@ -187,7 +189,18 @@ __device__ __forceinline__ void epilogue_row(const DenseParams& p, uint32_t acc,
         load_chunk(acc + b * 128 + j, g, true);
         load_chunk(acc + b * 128 + 64 + j, u, true);
         if (live) {
-          if (p.act == 1) {  // (the branch outside the loop: one of the two is compiled into each copy of it)
+          if (p.glu_limit > 0.f || p.glu_shift != 0.f) {
+            const float lim = p.glu_limit > 0.f ? p.glu_limit : CUDART_INF_F;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              g[e] = fminf(g[e], lim);
+              u[e] = fminf(fmaxf(u[e], -lim), lim) + p.glu_shift;
+            }
+          }
+          if (p.act == 2) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) g[e] = g[e] / (1.f + expf(-1.702f * g[e])) * u[e];
+          } else if (p.act == 1) {  // (the branch outside the loop: one of them is compiled into each copy of it)
 #pragma unroll
             for (int e = 0; e < 32; ++e) g[e] = 0.5f * g[e] * (1.f + tanhf(0.7978845608028654f * (g[e] + 0.044715f * g[e] * g[e] * g[e]))) * u[e];
           } else {
@@ -520,13 +533,17 @@ DLI_EXPORT int dli_dense_gemm_act(void* out, const void* x, const void* w, int t
   return launch_dense(p, x, w, tokens, features, K, stream);
 }
 
-// act [tokens, features / 2] = f(gate) * up (f: 0 silu, 1 gelu-tanh), for weights whose rows are interleaved in blocks of 64.
-DLI_EXPORT int dli_dense_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int gate_act, cudaStream_t stream) {
-  if (features % 128 || gate_act < 0 || gate_act > 1) return DLI_ERR_UNSUPPORTED;
+// act [tokens, features / 2] = f(min(gate, limit)) * (clamp(up, -limit, limit) + shift) (f: 0 silu, 1 gelu-tanh, 2 g * sigmoid(1.702 g);
+// limit 0: no bounds), for weights whose rows are interleaved in blocks of 64.
+DLI_EXPORT int dli_dense_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int gate_act, float limit, float shift,
+                                     cudaStream_t stream) {
+  if (features % 128 || gate_act < 0 || gate_act > 2 || limit < 0.f) return DLI_ERR_UNSUPPORTED;
   DenseParams p = {};
   p.out = (__nv_bfloat16*)act;
   p.mode = EP_SWIGLU;
   p.act = gate_act;
+  p.glu_limit = limit;
+  p.glu_shift = shift;
   return launch_dense(p, x, w, tokens, features, K, stream);
 }
 

@@ -228,3 +228,321 @@ DLI_EXPORT int dli_diff_attention_simt(void* out, const void* q, const void* k_p
 #undef DLI_DIFF
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- attention on tensor cores (bfloat16)
+// Compiled only with -DDIFF_DK=<dim> -DDIFF_DV=<vdim> (multiples of 16): one library per pair of sizes.
+//
+//   * a CTA owns a tile of up to 64 rows, a row being one (token, query head) pair, all of one KV head; warps 0-3 run
+//     map 1 of these rows, warps 4-7 map 2, sixteen rows a warp, on the SAME key and value tiles in shared memory: a key row
+//     of the cache holds both maps side by side, and the values are shared, so each is fetched once;
+//   * 64 keys a tile, copied in place from the pages by cp.async through the block table, double buffered; first the tiles of
+//     the kept first tokens that lie in front of the window, then the window's;
+//   * scores, running maximum, sums and outputs in float32 (online softmax), probabilities rounded to bfloat16 only as the
+//     operand of the P V product (mma.sync m16n8k16);
+//   * at the end the second map's warps leave their normalised output in shared memory, the first map's warps take the
+//     difference, norm the head, apply the gate and store.
+//   A sequence that brings one token is a tile of its KV group's heads; prompt portions and single tokens share the launch.
+#if defined(DIFF_DK) && defined(DIFF_DV)
+
+namespace tc {
+
+typedef __nv_bfloat16 bf16;
+constexpr int DK = DIFF_DK, DV = DIFF_DV;
+static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 256 && DV <= 256, "sizes must be multiples of 16 up to 256");
+constexpr int BLOCK_M = 64, BLOCK_N = 64, THREADS = 256;
+constexpr int KROW = 2 * DK * 2 + 16;  // bytes of a padded shared-memory row of queries or keys (both maps)
+constexpr int VROW = DV * 2 + 16;
+constexpr int KTILE = BLOCK_N * KROW, VTILE = BLOCK_N * VROW;
+constexpr int KCHUNKS = 2 * DK / 8, VCHUNKS = DV / 8;  // 16-byte chunks of a row
+constexpr int STAGE_BYTES = 2 * (KTILE + VTILE);
+constexpr int COMBINE_BYTES = BLOCK_M * (DV + 1) * 4;
+constexpr int SMEM_BYTES = BLOCK_M * KROW + (STAGE_BYTES > COMBINE_BYTES ? STAGE_BYTES : COMBINE_BYTES);
+
+struct Params {
+  bf16* out;           // [n, nh * DV]
+  const bf16* q;       // [n, nh * 2 * DK]
+  const bf16* k_pool;  // [pages, nkv, page_size, 2 DK]
+  const bf16* v_pool;  // [pages, nkv, page_size, DV]
+  const int* block_tables;
+  int max_blocks;
+  const int* q_start;
+  const int* kv_len;
+  const bf16* gate;
+  int gate_stride;
+  int nh, nkv, page_size, window, keep_first;
+  int tokens_per_tile, heads_per_chunk, head_chunks;
+  float scale_log2, lambda, post, eps;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS) diff_attention_tc_kernel(const Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* sQ = smem;
+  unsigned char* sK = smem + BLOCK_M * KROW;
+  unsigned char* sV = sK + 2 * KTILE;
+  float* sC = reinterpret_cast<float*>(sK);  // after the loop: the second map's outputs [BLOCK_M][DV + 1]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int map = warp >> 2, wrow = (warp & 3) * 16;
+  const int s = blockIdx.y, tile = blockIdx.x;
+  const int kvh = blockIdx.z / p.head_chunks, hc = blockIdx.z - kvh * p.head_chunks;
+  const int q0 = p.q_start[s];
+  const int qlen = p.q_start[s + 1] - q0;
+  const int tok0 = tile * p.tokens_per_tile;
+  if (tok0 >= qlen) return;
+  const int kvlen = p.kv_len[s];
+  const int ntok = min(p.tokens_per_tile, qlen - tok0);
+  const int G = p.nh / p.nkv, Gc = p.heads_per_chunk;
+  const int head0 = kvh * G + hc * Gc;
+  const int nheads = min(Gc, G - hc * Gc);
+  const int pos0 = kvlen - qlen + tok0;
+  const int rows_used = ntok * Gc;
+  const int* table = p.block_tables + (size_t)s * p.max_blocks;
+
+  // keys of the tile: the kept first tokens in front of the window, [0, kept), and the window's, [lo, hi)
+  const int hi = pos0 + ntok;
+  const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+  const int kept = min(p.keep_first, lo);
+  const int kept_tiles = (kept + BLOCK_N - 1) / BLOCK_N;
+  const int first_tile = max(lo / BLOCK_N, kept_tiles);
+  const int num_tiles = kept_tiles + max(0, (hi + BLOCK_N - 1) / BLOCK_N - first_tile);
+
+  for (int idx = tid; idx < BLOCK_M * KCHUNKS; idx += THREADS) {
+    const int r = idx / KCHUNKS, c = idx - r * KCHUNKS;
+    const int tok = r / Gc, hd = r - tok * Gc;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows_used && hd < nheads) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(q0 + tok0 + tok) * p.nh + head0 + hd) * 2 * DK + c * 8);
+    *reinterpret_cast<uint4*>(sQ + r * KROW + c * 16) = v;
+  }
+
+  auto load_tile = [&](int stage, int t) {
+    const int base = t * BLOCK_N;
+    unsigned char* dK = sK + stage * KTILE;
+    unsigned char* dV = sV + stage * VTILE;
+    for (int idx = tid; idx < BLOCK_N * (KCHUNKS + VCHUNKS); idx += THREADS) {
+      const int r = idx / (KCHUNKS + VCHUNKS), c = idx - r * (KCHUNKS + VCHUNKS);
+      const int key = base + r;
+      const bool ok = key < hi && (key >= lo || key < kept);
+      size_t at = 0;
+      if (ok) {
+        const int blk = key / p.page_size;
+        at = ((size_t)table[blk] * p.nkv + kvh) * p.page_size + (key - blk * p.page_size);
+      }
+      if (c < KCHUNKS) cp_async16(smem_u32(dK + r * KROW + c * 16), p.k_pool + (ok ? at * 2 * DK + c * 8 : 0), ok ? 16 : 0);
+      else cp_async16(smem_u32(dV + r * VROW + (c - KCHUNKS) * 16), p.v_pool + (ok ? at * DV + (c - KCHUNKS) * 8 : 0), ok ? 16 : 0);
+    }
+  };
+  auto tile_index = [&](int it) { return it < kept_tiles ? it : first_tile + (it - kept_tiles); };
+
+  const int r0 = wrow + (lane >> 2), r1 = r0 + 8;
+  const bool warp_active = wrow < rows_used;
+  int rpos[2];
+  bool rvalid[2];
+  {
+    const int t0 = r0 / Gc, t1 = r1 / Gc;
+    rvalid[0] = r0 < rows_used && (r0 - t0 * Gc) < nheads;
+    rvalid[1] = r1 < rows_used && (r1 - t1 * Gc) < nheads;
+    rpos[0] = pos0 + t0;
+    rpos[1] = pos0 + t1;
+  }
+  float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+  float o[DV / 8][4];
+#pragma unroll
+  for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  if (num_tiles > 0) load_tile(0, tile_index(0));
+  cp_async_commit();
+  for (int it = 0; it < num_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < num_tiles) load_tile(stage ^ 1, tile_index(it + 1));
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (warp_active) {
+      const unsigned char* wQ = sQ + wrow * KROW + map * DK * 2;
+      const unsigned char* tK = sK + stage * KTILE + map * DK * 2;
+      const unsigned char* tV = sV + stage * VTILE;
+      const int base = tile_index(it) * BLOCK_N;
+      float sc[BLOCK_N / 8][4];
+#pragma unroll
+      for (int j = 0; j < BLOCK_N / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < DK / 16; ++kk) {
+        uint32_t a[4];
+        ldsm4(a, smem_u32(wQ + (lane & 15) * KROW + (kk * 16 + (lane >> 4) * 8) * 2));
+#pragma unroll
+        for (int jp = 0; jp < BLOCK_N / 16; ++jp) {
+          uint32_t b[4];
+          const int key = jp * 16 + (lane & 7) + (lane >> 4) * 8;
+          const int dim = kk * 16 + ((lane >> 3) & 1) * 8;
+          ldsm4(b, smem_u32(tK + key * KROW + dim * 2));
+          mma16816(sc[2 * jp], a, b[0], b[1]);
+          mma16816(sc[2 * jp + 1], a, b[2], b[3]);
+        }
+      }
+      float tmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int j = 0; j < BLOCK_N / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int rr = e >> 1;
+          const int key = base + j * 8 + (lane & 3) * 2 + (e & 1);
+          bool ok = rvalid[rr] && key <= rpos[rr];
+          if (p.window > 0) ok = ok && (key > rpos[rr] - p.window || key < p.keep_first);
+          const float t = ok ? sc[j][e] * p.scale_log2 : -CUDART_INF_F;
+          sc[j][e] = t;
+          tmax[rr] = fmaxf(tmax[rr], t);
+        }
+      }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
+        const float mnew = fmaxf(m[rr], tmax[rr]);
+        msafe[rr] = (mnew == -CUDART_INF_F) ? 0.f : mnew;
+        corr[rr] = exp2f(m[rr] - msafe[rr]);
+        m[rr] = mnew;
+        l[rr] *= corr[rr];
+      }
+#pragma unroll
+      for (int j = 0; j < BLOCK_N / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = exp2f(sc[j][e] - msafe[e >> 1]);
+          sc[j][e] = pv;
+          l[e >> 1] += pv;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < DV / 8; ++j) {
+        o[j][0] *= corr[0]; o[j][1] *= corr[0];
+        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack2(sc[2 * kk][0], sc[2 * kk][1]);
+        a[1] = pack2(sc[2 * kk][2], sc[2 * kk][3]);
+        a[2] = pack2(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+        a[3] = pack2(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+        for (int jp = 0; jp < DV / 16; ++jp) {
+          uint32_t b[4];
+          const int key = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int dim = jp * 16 + (lane >> 4) * 8;
+          ldsm4t(b, smem_u32(tV + key * VROW + dim * 2));
+          mma16816(o[2 * jp], a, b[0], b[1]);
+          mma16816(o[2 * jp + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();  // the stage is overwritten by the copies issued next iteration
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+    l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+  }
+  const float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
+  if (map == 1 && warp_active) {
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      float* dst = sC + (rr ? r1 : r0) * (DV + 1);
+#pragma unroll
+      for (int j = 0; j < DV / 8; ++j) {
+        const int dim = j * 8 + (lane & 3) * 2;
+        dst[dim] = o[j][2 * rr] * inv[rr];
+        dst[dim + 1] = o[j][2 * rr + 1] * inv[rr];
+      }
+    }
+  }
+  __syncthreads();
+  if (map == 0 && warp_active) {
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int r = rr ? r1 : r0;
+      const float* other = sC + r * (DV + 1);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < DV / 8; ++j) {
+        const int dim = j * 8 + (lane & 3) * 2;
+        const float a = o[j][2 * rr] * inv[rr] - p.lambda * other[dim];
+        const float b = o[j][2 * rr + 1] * inv[rr] - p.lambda * other[dim + 1];
+        o[j][2 * rr] = a;
+        o[j][2 * rr + 1] = b;
+        ss = fmaf(a, a, fmaf(b, b, ss));
+      }
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      if (!rvalid[rr]) continue;
+      const int tok = r / Gc, hd = r - tok * Gc;
+      const size_t t = (size_t)(q0 + tok0 + tok);
+      const float g = p.gate != nullptr ? 1.f / (1.f + expf(-__bfloat162float(p.gate[t * p.gate_stride + head0 + hd]))) : 1.f;
+      const float f = rsqrtf(ss / (float)DV + p.eps) * p.post * g;
+      bf16* dst = p.out + (t * p.nh + head0 + hd) * DV;
+#pragma unroll
+      for (int j = 0; j < DV / 8; ++j) {
+        const int dim = j * 8 + (lane & 3) * 2;
+        *reinterpret_cast<__nv_bfloat162*>(dst + dim) = __floats2bfloat162_rn(o[j][2 * rr] * f, o[j][2 * rr + 1] * f);
+      }
+    }
+  }
+}
+
+}  // namespace tc
+
+DLI_EXPORT int dli_diff_attention_tc(void* out, const void* q, const void* k_pool, const void* v_pool, const int* block_tables, int max_blocks,
+                                     const int* q_start, const int* kv_len, int num_seqs, int max_q_len, const void* gate, int gate_stride,
+                                     int nh, int nkv, int page_size, int window, int keep_first, float scale, float lambda, float post, float eps,
+                                     cudaStream_t stream) {
+  using namespace tc;
+  if (num_seqs == 0 || max_q_len == 0) return 0;
+  if (nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
+  static OncePerDevice attr;
+  if (!attr.here()) {
+    cudaError_t e = cudaFuncSetAttribute(diff_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr.here() = true;
+  }
+  Params p;
+  p.out = (bf16*)out; p.q = (const bf16*)q; p.k_pool = (const bf16*)k_pool; p.v_pool = (const bf16*)v_pool;
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.q_start = q_start; p.kv_len = kv_len;
+  p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
+  p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window; p.keep_first = keep_first;
+  const int G = nh / nkv;
+  p.heads_per_chunk = G < BLOCK_M ? G : BLOCK_M;
+  p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
+  p.tokens_per_tile = BLOCK_M / p.heads_per_chunk;
+  p.scale_log2 = scale * 1.4426950408889634f; p.lambda = lambda; p.post = post; p.eps = eps;
+  const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
+  if (num_seqs > 65535 || nkv * p.head_chunks > 65535) return DLI_ERR_UNSUPPORTED;
+  launch_pdl(diff_attention_tc_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(THREADS), SMEM_BYTES, stream, 1, p);
+  return (int)cudaGetLastError();
+}
+#endif

@@ -133,7 +133,8 @@ struct Epilogue {
   const float* gain;
   float* out_ssq;
   int act;  // EP_STORE: an activation applied to the (bfloat16-rounded) sums before they are stored: 0 none, 1 relu^2, 2 gelu-tanh, 3 silu
-            // EP_SWIGLU: what is applied to the gate: 0 silu, 1 gelu-tanh
+            // EP_SWIGLU: what is applied to the gate: 0 silu, 1 gelu-tanh, 2 g * sigmoid(1.702 g)
+  float glu_limit, glu_shift;  // EP_SWIGLU: act(min(gate, limit)) * (clamp(up, -limit, limit) + shift); limit 0: no bounds
   const float* in_ssq;
   int in_tiles;
   float in_eps, in_inv_size;
@@ -162,11 +163,16 @@ __device__ __forceinline__ void fused_epilogue(const Epilogue& ep, void* out, co
   if (ep.mode == EP_SWIGLU) {
     const int I = features >> 1, col = tile * 64 + fl;
     if (fl < 64 && col < I) {
-      const float g = fin[fl], u = fin[fl + 64];
+      float g = fin[fl], u = fin[fl + 64];
+      if (ep.glu_limit > 0.f) {
+        g = fminf(g, ep.glu_limit);
+        u = fminf(fmaxf(u, -ep.glu_limit), ep.glu_limit);
+      }
       float a;
       if (ep.act == 1) a = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+      else if (ep.act == 2) a = g / (1.f + expf(-1.702f * g));
       else a = g / (1.f + expf(-g));
-      ((__nv_bfloat16*)out)[(size_t)t * I + col] = __float2bfloat16_rn(a * u);
+      ((__nv_bfloat16*)out)[(size_t)t * I + col] = __float2bfloat16_rn(a * (u + ep.glu_shift));
     }
     return;
   }
@@ -567,14 +573,18 @@ DLI_EXPORT int dli_skinny_gemm_act(void* out, const void* x, const void* w, int 
   return launch_skinny(out, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }
 
-// act[tokens, features / 2] = f(gate) * up (f: 0 silu, 1 gelu-tanh), for weights whose rows are interleaved in blocks of 64
+// act[tokens, features / 2] = f(min(gate, limit)) * (clamp(up, -limit, limit) + shift) (f: 0 silu, 1 gelu-tanh, 2 g * sigmoid(1.702 g);
+// limit 0: no bounds), for weights whose rows are interleaved in blocks of 64
 // (rows 128 j .. 128 j + 63: gate features 64 j .., rows 128 j + 64 .. 128 j + 127: the same up features).
 DLI_EXPORT int dli_skinny_gemm_swiglu(void* act, const void* x, const void* w, int tokens, int features, int K, int slices, int gate_act,
-                                      const float* in_ssq, int in_tiles, float in_eps, int in_size, cudaStream_t stream) {
-  if (features % 128 || gate_act < 0 || gate_act > 1) return DLI_ERR_UNSUPPORTED;
+                                      float limit, float shift, const float* in_ssq, int in_tiles, float in_eps, int in_size,
+                                      cudaStream_t stream) {
+  if (features % 128 || gate_act < 0 || gate_act > 2 || limit < 0.f) return DLI_ERR_UNSUPPORTED;
   Epilogue ep = {};
   ep.mode = EP_SWIGLU;
   ep.act = gate_act;
+  ep.glu_limit = limit;
+  ep.glu_shift = shift;
   if (!set_row_scale(ep, tokens, in_ssq, in_tiles, in_eps, in_size)) return DLI_ERR_UNSUPPORTED;
   return launch_skinny(act, 0, x, w, tokens, features, K, slices, 0, ep, stream);
 }

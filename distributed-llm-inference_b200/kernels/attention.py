@@ -118,7 +118,12 @@ def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_head
 def diff_attention(out: torch.Tensor, q: torch.Tensor, cache, batch, gate: torch.Tensor | None, num_heads: int, scale: float,
                    window: int | None, keep_first: int, lam: float, post: float, eps: float) -> None:
     """Differential attention of every token of the step over its sequence's pages (``ops.diff_attention_simt`` says what is
-    computed)."""
+    computed).  bfloat16 with sizes that are multiples of 16: the tensor-core kernel, one launch for portions and single
+    tokens; float32 and any other size: the CUDA-core kernel."""
     group = batch.group(cache.group)
+    if out.dtype == torch.bfloat16 and ops.diff_attention_tc_supported(cache.k.shape[3] // 2, cache.v.shape[3]):
+        ops.diff_attention_tc(out, q, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, batch.num_seqs, batch.max_q_len, gate,
+                              num_heads, scale, window, keep_first, lam, post, eps)
+        return
     ops.diff_attention_simt(out, q, cache.k, cache.v, group.block_tables, batch.seq_of_token, batch.positions, gate, num_heads, scale,
                             window, keep_first, lam, post, eps)

@@ -696,9 +696,9 @@ def skinny_gemm_residual(x, weight: torch.Tensor, h: torch.Tensor, gain: torch.T
     return ScaledRows(out, ssq, eps)
 
 
-def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor, activation: str = "silu") -> torch.Tensor:
-    """act(x Wg^T) * (x Wu^T) (act: silu or another of GLU_ACTIVATIONS) in one kernel: the decode matrix product with the activation in its
-    epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate rows, then the 64 up rows of
+def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor, activation: str = "silu", limit: float = 0.0, up_shift: float = 0.0) -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) (act: silu or another of GLU_ACTIVATIONS; bounds and shift as in ``silu_mul``) in one kernel: the decode matrix
+    product with the activation in its epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate rows, then the 64 up rows of
     the same features.  Returns bfloat16 [tokens, I]."""
     x, scale = _row_scale(x, "skinny_gemm_swiglu")
     _need(x, "x", torch.bfloat16), _need(weight_tiled, "weight", torch.bfloat16)
@@ -707,9 +707,9 @@ def skinny_gemm_swiglu(x: torch.Tensor, weight_tiled: torch.Tensor, activation: 
     if weight_tiled.shape[1] != K or features % 128 or not skinny_gemm_supported(tokens, K) or activation not in GLU_ACTIVATIONS:
         raise KernelError("skinny_gemm_swiglu: sizes or activation not supported")
     out = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
-    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int] + _ROW_SCALE_ARGS + [c_void_p])
-    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), GLU_ACTIVATIONS[activation], *scale,
-             _stream()), "skinny_gemm_swiglu")
+    f = _fn("skinny_gemm.cu", "dli_skinny_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float] + _ROW_SCALE_ARGS + [c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(weight_tiled), tokens, features, K, skinny_gemm_slices(tokens, features, K), GLU_ACTIVATIONS[activation],
+             float(limit), float(up_shift), *scale, _stream()), "skinny_gemm_swiglu")
     return out
 
 
@@ -813,15 +813,16 @@ def dense_gemm_act(x, weight: torch.Tensor, kind: str) -> torch.Tensor:
     return out
 
 
-def dense_gemm_swiglu(x, weight_tiled: torch.Tensor, activation: str = "silu") -> torch.Tensor:
-    """act(x Wg^T) * (x Wu^T) (act: silu or another of GLU_ACTIVATIONS) in the product's epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate
+def dense_gemm_swiglu(x, weight_tiled: torch.Tensor, activation: str = "silu", limit: float = 0.0, up_shift: float = 0.0) -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) (act: silu or another of GLU_ACTIVATIONS; bounds and shift as in ``silu_mul``) in the product's epilogue.  weight_tiled [2 I, K]: rows in blocks of 128 — 64 gate
     rows, then the 64 up rows of the same features.  Returns bfloat16 [tokens, I]."""
     tokens, features, K = _dense_sizes(x, weight_tiled, "dense_gemm_swiglu")
     if features % 128 or activation not in GLU_ACTIVATIONS:
         raise KernelError("dense_gemm_swiglu: the interleaved layout needs an intermediate size that is a multiple of 64, and a known activation")
     act = torch.empty((tokens, features // 2), dtype=torch.bfloat16, device=x.device)
-    f = _fn("dense_gemm.cu", "dli_dense_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(act), _ptr(x), _ptr(weight_tiled), tokens, features, K, GLU_ACTIVATIONS[activation], _stream()), "dense_gemm_swiglu")
+    f = _fn("dense_gemm.cu", "dli_dense_gemm_swiglu", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(_ptr(act), _ptr(x), _ptr(weight_tiled), tokens, features, K, GLU_ACTIVATIONS[activation], float(limit), float(up_shift), _stream()),
+           "dense_gemm_swiglu")
     return act
 
 
@@ -1320,3 +1321,34 @@ def diff_attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
     _check(f(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1], _ptr(seq_of_token), _ptr(positions),
              _ptr(gate), gate_stride, n, num_heads, nkv, d2 // 2, vdim, page_size, int(window or 0), int(keep_first), float(scale), float(lam),
              float(post), float(eps), DT_CODE[out.dtype], _stream()), "diff_attention_simt")
+
+
+def diff_attention_tc_supported(dim: int, vdim: int) -> bool:
+    """Sizes of a map's keys and of the values that the tensor-core kernel of differential attention takes (bfloat16)."""
+    fits = 64 * (12 * dim + 4 * vdim + 80) <= 227 * 1024  # 64 query rows and two stages of 64 key and value rows in shared memory
+    return dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 256 and 16 <= vdim <= 256 and fits
+
+
+def diff_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
+                      q_start: torch.Tensor, kv_len: torch.Tensor, num_seqs: int, max_q_len: int, gate: torch.Tensor | None, num_heads: int,
+                      scale: float, window: int | None, keep_first: int, lam: float, post: float, eps: float) -> None:
+    """``diff_attention_simt`` on tensor cores (bfloat16; one library per pair of sizes): sequences given by their first rows
+    ``q_start`` [seqs + 1] and lengths in the cache after this step ``kv_len`` [seqs]; prompt portions and single tokens in one
+    launch, sized for ``max_q_len`` rows a sequence."""
+    _need(out, "out", torch.bfloat16), _need(q, "q", torch.bfloat16), _need(k_pool, "k_pool", torch.bfloat16), _need(v_pool, "v_pool", torch.bfloat16)
+    n = q.shape[0]
+    _, nkv, page_size, d2 = k_pool.shape
+    vdim = v_pool.shape[3]
+    if not diff_attention_tc_supported(d2 // 2, vdim) or tuple(q.shape) != (n, num_heads * d2) or tuple(out.shape) != (n, num_heads * vdim) or num_heads % nkv:
+        raise KernelError("diff_attention_tc: shapes do not agree or sizes not supported")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != out.dtype or gate.shape != (n, num_heads) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("diff_attention_tc: gate must be [n, heads] with unit column stride")
+        gate_stride = gate.stride(0)
+    f = _fn("diff_attention.cu", "dli_diff_attention_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
+                                                           c_void_p], defines={"DIFF_DK": d2 // 2, "DIFF_DV": vdim})
+    _check(f(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1], _ptr(q_start), _ptr(kv_len), int(num_seqs),
+             int(max_q_len), _ptr(gate), gate_stride, num_heads, nkv, page_size, int(window or 0), int(keep_first), float(scale), float(lam),
+             float(post), float(eps), _stream()), "diff_attention_tc")

@@ -34,7 +34,6 @@ class SwiGLU(Part):
             raise ValueError(f"activation {self.activation!r} is not supported (known: {sorted(ops.GLU_ACTIVATIONS)})")
         self.limit = float(spec.params.get("limit") or 0.0)
         self.up_shift = float(spec.params.get("up_shift") or 0.0)
-        self.plain_glu = self.limit == 0.0 and self.up_shift == 0.0 and self.activation in ("silu", "gelu_tanh")  # what the products' epilogues take
         self.names = {role: tensor_name(spec, role, role + "_proj.weight") for role in ("gate", "up", "down")}
         self.w_gate_up: torch.Tensor | None = None
         self.tiled = False
@@ -59,10 +58,10 @@ class SwiGLU(Part):
         self.w_down = tensors[self.names["down"]]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.tiled and self.plain_glu and fused_epilogue(x):
-            act = ops.skinny_gemm_swiglu(x, self.w_gate_up, self.activation)
-        elif self.tiled and self.plain_glu and dense_product(x, 2 * self.inter, "swiglu"):
-            act = ops.dense_gemm_swiglu(x, self.w_gate_up, self.activation)
+        if self.tiled and fused_epilogue(x):
+            act = ops.skinny_gemm_swiglu(x, self.w_gate_up, self.activation, self.limit, self.up_shift)
+        elif self.tiled and dense_product(x, 2 * self.inter, "swiglu"):
+            act = ops.dense_gemm_swiglu(x, self.w_gate_up, self.activation, self.limit, self.up_shift)
         else:
             gate_up = project(x, self.w_gate_up)
             act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)

@@ -362,10 +362,10 @@ def skinny_gemm_residual(x, weight, h, gain, eps, slices=None):
     return ops.ScaledRows((h * gain).to(torch.bfloat16), sq.view(tokens, tiles, 128).sum(-1), eps)
 
 
-def skinny_gemm_swiglu(x, weight_tiled, activation="silu"):
+def skinny_gemm_swiglu(x, weight_tiled, activation="silu", limit=0.0, up_shift=0.0):
     y = _sums(x, weight_tiled)
     out = torch.empty((y.shape[0], y.shape[1] // 2), dtype=torch.bfloat16)
-    silu_mul(out, y, tiled=True, activation=activation)
+    silu_mul(out, y, True, activation, limit, up_shift)
     return out
 
 
@@ -395,8 +395,8 @@ def dense_gemm_act(x, weight, kind):
     return skinny_gemm_act(x, weight, kind)
 
 
-def dense_gemm_swiglu(x, weight_tiled, activation="silu"):
-    return skinny_gemm_swiglu(x, weight_tiled, activation)
+def dense_gemm_swiglu(x, weight_tiled, activation="silu", limit=0.0, up_shift=0.0):
+    return skinny_gemm_swiglu(x, weight_tiled, activation, limit, up_shift)
 
 
 def dense_gemm_rotary(x, wqkv, table, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, rotary_dim, page_size, write_kv):
@@ -573,6 +573,15 @@ def diff_attention_simt(out, q, k_pool, v_pool, block_tables, seq_of_token, posi
             out[t, h * vdim : (h + 1) * vdim] = o.to(out.dtype)
 
 
+def diff_attention_tc(out, q, k_pool, v_pool, block_tables, q_start, kv_len, num_seqs, max_q_len, gate, num_heads, scale, window, keep_first, lam,
+                      post, eps):
+    lens = (q_start[1:] - q_start[:-1]).long()
+    seq = torch.repeat_interleave(torch.arange(num_seqs), lens)
+    at = torch.arange(q.shape[0])
+    positions = (kv_len.long() - lens)[seq] + at - q_start.long()[seq]
+    diff_attention_simt(out, q, k_pool, v_pool, block_tables, seq, positions, gate, num_heads, scale, window, keep_first, lam, post, eps)
+
+
 OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_page, "add_rmsnorm": add_rmsnorm,
        "rotary_table": rotary_table, "rotary_store": rotary_store, "silu_mul": silu_mul, "paged_attention_simt": paged_attention_simt,
        "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
@@ -585,7 +594,8 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "add_rmsnorm_pair": add_rmsnorm_pair, "scale_softcap": scale_softcap, "latent_prep": latent_prep, "delta_rule_scan": delta_rule_scan,
        "heads_matvec": heads_matvec, "heads_matvec_supported": lambda in_features, features: True,
        "pair_embedding": pair_embedding, "group_norm_add": group_norm_add, "group_norm_rows": group_norm_rows, "gelu_mul_rows": gelu_mul_rows,
-       "depth_average": depth_average, "mingru_scan": mingru_scan, "diff_prep": diff_prep, "diff_attention_simt": diff_attention_simt}
+       "depth_average": depth_average, "mingru_scan": mingru_scan, "diff_prep": diff_prep, "diff_attention_simt": diff_attention_simt,
+       "diff_attention_tc": diff_attention_tc}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered

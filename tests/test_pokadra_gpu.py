@@ -158,11 +158,12 @@ def test_diff_attention_kernels(dtype, nh, nkv, dim, vdim, rot, page, window, ke
     from dli_b200.kernels import ops
 
     lens, starts = (37, 1, 9), (0, 50, 37)  # sequence 0 twice: a first portion, later nine more tokens; sequence 1 decodes at position 50
-    pages = 24
+    per_seq = -(-52 // page)
+    pages = 2 * per_seq
     order = np.random.default_rng(0).permutation(pages)
     k_pool = torch.full((pages, nkv, page, 2 * dim), float("nan"), dtype=dtype, device="cuda")
     v_pool = torch.full((pages, nkv, page, vdim), float("nan"), dtype=dtype, device="cuda")
-    tables = torch.tensor(np.stack([order[:12], order[12:24]]), dtype=torch.int32)
+    tables = torch.tensor(np.stack([order[:per_seq], order[per_seq:]]), dtype=torch.int32)
     cols = nh * 2 * dim + nkv * (2 * dim + vdim) + nh
     wq, wk = _rand((dim,), torch.float32, 1) + 1.5, _rand((dim,), torch.float32, 2) + 1.5
     freq = torch.tensor([10000.0 ** (-2 * i / max(rot, 2)) for i in range(max(rot // 2, 1))], dtype=torch.float32).cuda()
@@ -215,3 +216,12 @@ def test_bounded_gate_times_shifted_up_kernel(dtype):
         ops.silu_mul(out, gu, tiled, "quick_gelu", 1.2, 1.0)
         cpu_ops.silu_mul(ref, gu.cpu(), tiled, "quick_gelu", 1.2, 1.0)
         assert torch.allclose(out.float().cpu(), ref.float(), atol=1e-5 if dtype == torch.float32 else 3e-2)
+    # the same in the epilogues of the two products that yield gate and up (bfloat16): a decode step's few tokens and a long portion,
+    # with sums large enough for both bounds to act
+    if dtype == torch.bfloat16:
+        for tokens in (3, 700):
+            x, wt = _rand((tokens, 256), dtype, 6, 0.5), _rand((384, 256), dtype, 7, 0.3)
+            want = cpu_ops.skinny_gemm_swiglu(x.cpu(), wt.cpu(), "quick_gelu", 1.2, 1.0)
+            got = (ops.skinny_gemm_swiglu if tokens <= 8 else ops.dense_gemm_swiglu)(x, wt, "quick_gelu", 1.2, 1.0)
+            assert (want.float().abs() > 1.9).any()  # some gate and up at their bounds: 1.2 sigmoid(1.702 * 1.2) * 2.2 = 2.3
+            assert torch.allclose(got.float().cpu(), want.float(), atol=3e-2, rtol=2e-2)
