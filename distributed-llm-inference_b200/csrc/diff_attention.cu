@@ -233,14 +233,18 @@ DLI_EXPORT int dli_diff_attention_simt(void* out, const void* q, const void* k_p
 // Compiled only with -DDIFF_DK=<dim> -DDIFF_DV=<vdim> (multiples of 16): one library per pair of sizes.
 //
 //   * a CTA owns a tile of up to 64 rows, a row being one (token, query head) pair, all of one KV head; warps 0-3 run
-//     map 1 of these rows, warps 4-7 map 2, sixteen rows a warp, on the SAME key and value tiles in shared memory: a key row
-//     of the cache holds both maps side by side, and the values are shared, so each is fetched once;
+//     map 1 of these rows, warps 4-7 map 2, on the SAME key and value tiles in shared memory: a key row of the cache holds
+//     both maps side by side, and the values are shared, so each is fetched once;
+//   * the four warps of a map divide the tile between them by rows and keys: 4 x 16 rows with all 64 keys of a key tile
+//     each, or, when the CTA has no more than 32 (16) rows — a short portion, a single decoded token with its KV group's
+//     heads —, 2 (1) x 16 rows with 32 (16) keys each, so that no warp idles while a single token walks a long window;
 //   * 64 keys a tile, copied in place from the pages by cp.async through the block table, double buffered; first the tiles of
 //     the kept first tokens that lie in front of the window, then the window's;
 //   * scores, running maximum, sums and outputs in float32 (online softmax), probabilities rounded to bfloat16 only as the
-//     operand of the P V product (mma.sync m16n8k16);
-//   * at the end the second map's warps leave their normalised output in shared memory, the first map's warps take the
-//     difference, norm the head, apply the gate and store.
+//     operand of the P V product (mma.sync m16n8k16); a key tile that every row of the warp sees whole skips the mask, and
+//     the running output is rescaled only when some row's maximum has grown;
+//   * at the end every warp leaves its unnormalised output, maximum and sum in shared memory; a warp per row then merges the
+//     key ranges of each map, takes the difference, norms the head, applies the gate and stores whole rows.
 //   A sequence that brings one token is a tile of its KV group's heads; prompt portions and single tokens share the launch.
 #if defined(DIFF_DK) && defined(DIFF_DV)
 
@@ -249,14 +253,16 @@ namespace tc {
 typedef __nv_bfloat16 bf16;
 constexpr int DK = DIFF_DK, DV = DIFF_DV;
 static_assert(DK % 16 == 0 && DV % 16 == 0 && DK >= 16 && DV >= 16 && DK <= 256 && DV <= 256, "sizes must be multiples of 16 up to 256");
-constexpr int BLOCK_M = 64, BLOCK_N = 64, THREADS = 256;
+constexpr int BLOCK_M = 64, BLOCK_N = 64, THREADS = 256, WARPS = THREADS / 32;
 constexpr int KROW = 2 * DK * 2 + 16;  // bytes of a padded shared-memory row of queries or keys (both maps)
 constexpr int VROW = DV * 2 + 16;
 constexpr int KTILE = BLOCK_N * KROW, VTILE = BLOCK_N * VROW;
 constexpr int KCHUNKS = 2 * DK / 8, VCHUNKS = DV / 8;  // 16-byte chunks of a row
 constexpr int STAGE_BYTES = 2 * (KTILE + VTILE);
-constexpr int COMBINE_BYTES = BLOCK_M * (DV + 1) * 4;
+constexpr int PROW = DV + (DV % 32 == 0 ? 8 : 24);  // floats of a row of partial results: DV outputs, maximum, sum; 8 mod 32 keeps the float2 stores apart
+constexpr int COMBINE_BYTES = WARPS * 16 * PROW * 4;
 constexpr int SMEM_BYTES = BLOCK_M * KROW + (STAGE_BYTES > COMBINE_BYTES ? STAGE_BYTES : COMBINE_BYTES);
+constexpr int MIN_CTAS = (DK <= 128 && DV <= 128 && 2 * SMEM_BYTES + 2048 <= 227 * 1024) ? 2 : 1;  // two CTAs an SM where 128 registers a thread suffice
 
 struct Params {
   bf16* out;           // [n, nh * DV]
@@ -272,6 +278,8 @@ struct Params {
   int nh, nkv, page_size, window, keep_first;
   int tokens_per_tile, heads_per_chunk, head_chunks;
   float scale_log2, lambda, post, eps;
+  int splits;      // > 1: single tokens only, the key tiles of each divided between `splits` CTAs, partial results in scratch
+  float* scratch;  // [rows of (sequence, head)][splits][2 maps][DV + 2]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -295,105 +303,86 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(THREADS) diff_attention_tc_kernel(const Params p) {
-  pdl_launch_dependents();
-  pdl_wait();
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* sQ = smem;
-  unsigned char* sK = smem + BLOCK_M * KROW;
-  unsigned char* sV = sK + 2 * KTILE;
-  float* sC = reinterpret_cast<float*>(sK);  // after the loop: the second map's outputs [BLOCK_M][DV + 1]
+// What a CTA knows of its tile.
+struct Tile {
+  int pos0, rows_used, Gc, nheads, hi, lo, kept, kept_tiles, first_tile, num_tiles, kvh;
+  int it0, it1;  // the CTA's share of the key tiles (all of them unless single tokens' keys are split between CTAs)
+  const int* table;
+};
 
+// The walk over the key tiles with the map's four warps arranged as (4 / KS) row tiles x KS key ranges.  Leaves every active
+// warp's unnormalised output, maximum and sum in `part` (which overlays the key and value stages).
+template <int KS>
+__device__ __forceinline__ void walk(const Params& p, const Tile& T, unsigned char* sQ, unsigned char* sK, unsigned char* sV, float* part) {
+  constexpr int NKEYS = BLOCK_N / KS;  // keys of a tile that one warp takes
+  constexpr int NJ = NKEYS / 8, NKK = NKEYS / 16;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int map = warp >> 2, wrow = (warp & 3) * 16;
-  const int s = blockIdx.y, tile = blockIdx.x;
-  const int kvh = blockIdx.z / p.head_chunks, hc = blockIdx.z - kvh * p.head_chunks;
-  const int q0 = p.q_start[s];
-  const int qlen = p.q_start[s + 1] - q0;
-  const int tok0 = tile * p.tokens_per_tile;
-  if (tok0 >= qlen) return;
-  const int kvlen = p.kv_len[s];
-  const int ntok = min(p.tokens_per_tile, qlen - tok0);
-  const int G = p.nh / p.nkv, Gc = p.heads_per_chunk;
-  const int head0 = kvh * G + hc * Gc;
-  const int nheads = min(Gc, G - hc * Gc);
-  const int pos0 = kvlen - qlen + tok0;
-  const int rows_used = ntok * Gc;
-  const int* table = p.block_tables + (size_t)s * p.max_blocks;
+  const int map = warp >> 2, w4 = warp & 3;
+  const int wrow = (w4 / KS) * 16, koff = (w4 % KS) * NKEYS;
+  const bool warp_active = wrow < T.rows_used;
+  const int Gc = T.Gc;
 
-  // keys of the tile: the kept first tokens in front of the window, [0, kept), and the window's, [lo, hi)
-  const int hi = pos0 + ntok;
-  const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
-  const int kept = min(p.keep_first, lo);
-  const int kept_tiles = (kept + BLOCK_N - 1) / BLOCK_N;
-  const int first_tile = max(lo / BLOCK_N, kept_tiles);
-  const int num_tiles = kept_tiles + max(0, (hi + BLOCK_N - 1) / BLOCK_N - first_tile);
-
-  for (int idx = tid; idx < BLOCK_M * KCHUNKS; idx += THREADS) {
-    const int r = idx / KCHUNKS, c = idx - r * KCHUNKS;
-    const int tok = r / Gc, hd = r - tok * Gc;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rows_used && hd < nheads) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(q0 + tok0 + tok) * p.nh + head0 + hd) * 2 * DK + c * 8);
-    *reinterpret_cast<uint4*>(sQ + r * KROW + c * 16) = v;
-  }
-
+  // four threads a key row: one look into the block table, then the row's 16-byte chunks in turn
   auto load_tile = [&](int stage, int t) {
-    const int base = t * BLOCK_N;
-    unsigned char* dK = sK + stage * KTILE;
-    unsigned char* dV = sV + stage * VTILE;
-    for (int idx = tid; idx < BLOCK_N * (KCHUNKS + VCHUNKS); idx += THREADS) {
-      const int r = idx / (KCHUNKS + VCHUNKS), c = idx - r * (KCHUNKS + VCHUNKS);
-      const int key = base + r;
-      const bool ok = key < hi && (key >= lo || key < kept);
-      size_t at = 0;
-      if (ok) {
-        const int blk = key / p.page_size;
-        at = ((size_t)table[blk] * p.nkv + kvh) * p.page_size + (key - blk * p.page_size);
-      }
-      if (c < KCHUNKS) cp_async16(smem_u32(dK + r * KROW + c * 16), p.k_pool + (ok ? at * 2 * DK + c * 8 : 0), ok ? 16 : 0);
-      else cp_async16(smem_u32(dV + r * VROW + (c - KCHUNKS) * 16), p.v_pool + (ok ? at * DV + (c - KCHUNKS) * 8 : 0), ok ? 16 : 0);
+    const int r = tid >> 2, key = t * BLOCK_N + r;
+    const bool ok = key < T.hi && (key >= T.lo || key < T.kept);
+    size_t at = 0;
+    if (ok) {
+      const int blk = key / p.page_size;
+      at = ((size_t)T.table[blk] * p.nkv + T.kvh) * p.page_size + (key - blk * p.page_size);
+    }
+    const bf16* gK = p.k_pool + at * 2 * DK;
+    const bf16* gV = p.v_pool + at * DV;
+    const uint32_t dK = smem_u32(sK + stage * KTILE + r * KROW), dV = smem_u32(sV + stage * VTILE + r * VROW);
+    const int bytes = ok ? 16 : 0;  // 0: the chunk is filled with zeros and nothing is read
+#pragma unroll
+    for (int i = 0; i < (KCHUNKS + VCHUNKS + 3) / 4; ++i) {
+      const int c = (tid & 3) + 4 * i;
+      if (c < KCHUNKS) cp_async16(dK + c * 16, gK + c * 8, bytes);
+      else if (c < KCHUNKS + VCHUNKS) cp_async16(dV + (c - KCHUNKS) * 16, gV + (c - KCHUNKS) * 8, bytes);
     }
   };
-  auto tile_index = [&](int it) { return it < kept_tiles ? it : first_tile + (it - kept_tiles); };
+  auto tile_index = [&](int it) { return it < T.kept_tiles ? it : T.first_tile + (it - T.kept_tiles); };
 
   const int r0 = wrow + (lane >> 2), r1 = r0 + 8;
-  const bool warp_active = wrow < rows_used;
   int rpos[2];
   bool rvalid[2];
   {
     const int t0 = r0 / Gc, t1 = r1 / Gc;
-    rvalid[0] = r0 < rows_used && (r0 - t0 * Gc) < nheads;
-    rvalid[1] = r1 < rows_used && (r1 - t1 * Gc) < nheads;
-    rpos[0] = pos0 + t0;
-    rpos[1] = pos0 + t1;
+    rvalid[0] = r0 < T.rows_used && (r0 - t0 * Gc) < T.nheads;
+    rvalid[1] = r1 < T.rows_used && (r1 - t1 * Gc) < T.nheads;
+    rpos[0] = T.pos0 + t0;
+    rpos[1] = T.pos0 + t1;
   }
+  // positions of the warp's first and last token: a key range at or below the first and inside the last one's window is seen whole
+  const int pos_min = T.pos0 + wrow / Gc, pos_max = T.pos0 + min(wrow + 15, T.rows_used - 1) / Gc;
   float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
   float o[DV / 8][4];
 #pragma unroll
   for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  if (num_tiles > 0) load_tile(0, tile_index(0));
+  if (T.it0 < T.it1) load_tile(0, tile_index(T.it0));
   cp_async_commit();
-  for (int it = 0; it < num_tiles; ++it) {
-    const int stage = it & 1;
-    if (it + 1 < num_tiles) load_tile(stage ^ 1, tile_index(it + 1));
+  for (int it = T.it0; it < T.it1; ++it) {
+    const int stage = (it - T.it0) & 1;
+    if (it + 1 < T.it1) load_tile(stage ^ 1, tile_index(it + 1));
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
     if (warp_active) {
       const unsigned char* wQ = sQ + wrow * KROW + map * DK * 2;
-      const unsigned char* tK = sK + stage * KTILE + map * DK * 2;
-      const unsigned char* tV = sV + stage * VTILE;
-      const int base = tile_index(it) * BLOCK_N;
-      float sc[BLOCK_N / 8][4];
+      const unsigned char* tK = sK + stage * KTILE + koff * KROW + map * DK * 2;
+      const unsigned char* tV = sV + stage * VTILE + koff * VROW;
+      const int base = tile_index(it) * BLOCK_N + koff;
+      float sc[NJ][4];
 #pragma unroll
-      for (int j = 0; j < BLOCK_N / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+      for (int j = 0; j < NJ; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < DK / 16; ++kk) {
         uint32_t a[4];
         ldsm4(a, smem_u32(wQ + (lane & 15) * KROW + (kk * 16 + (lane >> 4) * 8) * 2));
 #pragma unroll
-        for (int jp = 0; jp < BLOCK_N / 16; ++jp) {
+        for (int jp = 0; jp < NKK; ++jp) {
           uint32_t b[4];
           const int key = jp * 16 + (lane & 7) + (lane >> 4) * 8;
           const int dim = kk * 16 + ((lane >> 3) & 1) * 8;
@@ -403,32 +392,54 @@ __global__ void __launch_bounds__(THREADS) diff_attention_tc_kernel(const Params
         }
       }
       float tmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
+      const bool whole = base + NKEYS - 1 <= pos_min && (p.window <= 0 || base > pos_max - p.window || base + NKEYS <= p.keep_first);
+      if (whole) {
 #pragma unroll
-      for (int j = 0; j < BLOCK_N / 8; ++j) {
+        for (int j = 0; j < NJ; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int rr = e >> 1;
-          const int key = base + j * 8 + (lane & 3) * 2 + (e & 1);
-          bool ok = rvalid[rr] && key <= rpos[rr];
-          if (p.window > 0) ok = ok && (key > rpos[rr] - p.window || key < p.keep_first);
-          const float t = ok ? sc[j][e] * p.scale_log2 : -CUDART_INF_F;
-          sc[j][e] = t;
-          tmax[rr] = fmaxf(tmax[rr], t);
+          for (int e = 0; e < 4; ++e) {
+            sc[j][e] *= p.scale_log2;
+            tmax[e >> 1] = fmaxf(tmax[e >> 1], sc[j][e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int rr = e >> 1;
+            const int key = base + j * 8 + (lane & 3) * 2 + (e & 1);
+            bool ok = rvalid[rr] && key <= rpos[rr];
+            if (p.window > 0) ok = ok && (key > rpos[rr] - p.window || key < p.keep_first);
+            const float t = ok ? sc[j][e] * p.scale_log2 : -CUDART_INF_F;
+            sc[j][e] = t;
+            tmax[rr] = fmaxf(tmax[rr], t);
+          }
         }
       }
       float corr[2], msafe[2];
+      bool grew = false;
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
         tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
         const float mnew = fmaxf(m[rr], tmax[rr]);
+        grew = grew || mnew > m[rr];
         msafe[rr] = (mnew == -CUDART_INF_F) ? 0.f : mnew;
         corr[rr] = exp2f(m[rr] - msafe[rr]);
         m[rr] = mnew;
-        l[rr] *= corr[rr];
+      }
+      if (__any_sync(0xffffffffu, grew)) {  // else both factors are 1 in every lane
+        l[0] *= corr[0];
+        l[1] *= corr[1];
+#pragma unroll
+        for (int j = 0; j < DV / 8; ++j) {
+          o[j][0] *= corr[0]; o[j][1] *= corr[0];
+          o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        }
       }
 #pragma unroll
-      for (int j = 0; j < BLOCK_N / 8; ++j) {
+      for (int j = 0; j < NJ; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float pv = exp2f(sc[j][e] - msafe[e >> 1]);
@@ -437,12 +448,7 @@ __global__ void __launch_bounds__(THREADS) diff_attention_tc_kernel(const Params
         }
       }
 #pragma unroll
-      for (int j = 0; j < DV / 8; ++j) {
-        o[j][0] *= corr[0]; o[j][1] *= corr[0];
-        o[j][2] *= corr[1]; o[j][3] *= corr[1];
-      }
-#pragma unroll
-      for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+      for (int kk = 0; kk < NKK; ++kk) {
         uint32_t a[4];
         a[0] = pack2(sc[2 * kk][0], sc[2 * kk][1]);
         a[1] = pack2(sc[2 * kk][2], sc[2 * kk][3]);
@@ -462,57 +468,180 @@ __global__ void __launch_bounds__(THREADS) diff_attention_tc_kernel(const Params
     __syncthreads();  // the stage is overwritten by the copies issued next iteration
   }
   cp_async_wait<0>();
+  __syncthreads();  // the stages are free: the partial results go where they were
+
+  if (warp_active) {
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
+      l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
+      float* dst = part + ((size_t)warp * 16 + (lane >> 2) + 8 * rr) * PROW;
+#pragma unroll
+      for (int j = 0; j < DV / 8; ++j) *reinterpret_cast<float2*>(dst + j * 8 + (lane & 3) * 2) = make_float2(o[j][2 * rr], o[j][2 * rr + 1]);
+      if ((lane & 3) == 0) {
+        dst[DV] = m[rr];
+        dst[DV + 1] = l[rr];
+      }
+    }
+  }
+}
+
+constexpr int NC = (DV + 63) / 64;  // pairs of outputs a lane holds when a warp holds a row
+constexpr int SROW = DV + 2;         // floats of one map's partial result in the scratch of split keys: outputs, maximum, sum
+
+// A warp merges `count` partial results of one row and map, `stride` floats apart, each DV unnormalised outputs followed by
+// its maximum (in units of log2) and its sum: the merged outputs (still unnormalised), their maximum and sum.
+__device__ __forceinline__ void merge_partials(const float* src, size_t stride, int count, int lane, float (&val)[NC][2], float& mx, float& sum) {
+  mx = -CUDART_INF_F;
+  for (int i = 0; i < count; ++i) mx = fmaxf(mx, src[i * stride + DV]);
+  sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) val[c][0] = val[c][1] = 0.f;
+  for (int i = 0; i < count; ++i) {
+    const float* pr = src + i * stride;
+    const float mi = pr[DV];
+    const float f = mi == -CUDART_INF_F ? 0.f : exp2f(mi - mx);  // a key range in which the row saw nothing
+    sum = fmaf(f, pr[DV + 1], sum);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int d = c * 64 + lane * 2;
+      if (d < DV) {
+        const float2 v = *reinterpret_cast<const float2*>(pr + d);
+        val[c][0] = fmaf(f, v.x, val[c][0]);
+        val[c][1] = fmaf(f, v.y, val[c][1]);
+      }
+    }
+  }
+}
+
+// The end of a row: a1 / l1 - lambda a2 / l2, the head's norm, the gate, and the store.
+__device__ __forceinline__ void finish_row(const Params& p, float (&v1)[NC][2], const float (&v2)[NC][2], float l1, float l2, size_t t, int head,
+                                           int lane) {
+  const float i1 = l1 > 0.f ? 1.f / l1 : 0.f, i2 = l2 > 0.f ? p.lambda / l2 : 0.f;
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const float a = v1[c][0] * i1 - v2[c][0] * i2, b = v1[c][1] * i1 - v2[c][1] * i2;
+    v1[c][0] = a;
+    v1[c][1] = b;
+    ss = fmaf(a, a, fmaf(b, b, ss));  // lanes beyond DV hold zeros
+  }
+  ss = warp_sum(ss);
+  const float g = p.gate != nullptr ? 1.f / (1.f + expf(-__bfloat162float(p.gate[t * p.gate_stride + head]))) : 1.f;
+  const float f = rsqrtf(ss / (float)DV + p.eps) * p.post * g;
+  bf16* dst = p.out + (t * p.nh + head) * DV;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int d = c * 64 + lane * 2;
+    if (d < DV) *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(v1[c][0] * f, v1[c][1] * f);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, MIN_CTAS) diff_attention_tc_kernel(const Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* sQ = smem;
+  unsigned char* sK = smem + BLOCK_M * KROW;
+  unsigned char* sV = sK + 2 * KTILE;
+  float* part = reinterpret_cast<float*>(sK);  // after the walk: [WARPS][16][PROW]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int s = blockIdx.y;
+  const int tile = p.splits > 1 ? 0 : blockIdx.x, split = p.splits > 1 ? blockIdx.x : 0;
+  const int kvh = blockIdx.z / p.head_chunks, hc = blockIdx.z - kvh * p.head_chunks;
+  const int q0 = p.q_start[s];
+  const int qlen = p.q_start[s + 1] - q0;
+  const int tok0 = tile * p.tokens_per_tile;
+  if (tok0 >= qlen) return;
+  const int kvlen = p.kv_len[s];
+  const int ntok = min(p.tokens_per_tile, qlen - tok0);
+  const int G = p.nh / p.nkv, Gc = p.heads_per_chunk;
+  const int head0 = kvh * G + hc * Gc;
+  Tile T;
+  T.Gc = Gc;
+  T.kvh = kvh;
+  T.nheads = min(Gc, G - hc * Gc);
+  T.pos0 = kvlen - qlen + tok0;
+  T.rows_used = ntok * Gc;
+  T.table = p.block_tables + (size_t)s * p.max_blocks;
+  // keys of the tile: the kept first tokens in front of the window, [0, kept), and the window's, [lo, hi)
+  T.hi = T.pos0 + ntok;
+  T.lo = (p.window > 0 && T.pos0 - p.window + 1 > 0) ? T.pos0 - p.window + 1 : 0;
+  T.kept = min(p.keep_first, T.lo);
+  T.kept_tiles = (T.kept + BLOCK_N - 1) / BLOCK_N;
+  T.first_tile = max(T.lo / BLOCK_N, T.kept_tiles);
+  T.num_tiles = T.kept_tiles + max(0, (T.hi + BLOCK_N - 1) / BLOCK_N - T.first_tile);
+  T.it0 = 0;
+  T.it1 = T.num_tiles;
+  if (p.splits > 1) {  // single tokens only: CTA `split` walks its share of the key tiles, possibly none
+    const int per = (T.num_tiles + p.splits - 1) / p.splits;
+    T.it0 = min(T.num_tiles, split * per);
+    T.it1 = min(T.num_tiles, T.it0 + per);
+  }
+
+  for (int idx = tid; idx < BLOCK_M * KCHUNKS; idx += THREADS) {
+    const int r = idx / KCHUNKS, c = idx - r * KCHUNKS;
+    const int tok = r / Gc, hd = r - tok * Gc;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < T.rows_used && hd < T.nheads) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(q0 + tok0 + tok) * p.nh + head0 + hd) * 2 * DK + c * 8);
+    *reinterpret_cast<uint4*>(sQ + r * KROW + c * 16) = v;
+  }
+
+  int KS;
+  if (T.rows_used <= 16) {
+    KS = 4;
+    walk<4>(p, T, sQ, sK, sV, part);
+  } else if (T.rows_used <= 32) {
+    KS = 2;
+    walk<2>(p, T, sQ, sK, sV, part);
+  } else {
+    KS = 1;
+    walk<1>(p, T, sQ, sK, sV, part);
+  }
   __syncthreads();
 
+  // a warp per row: merge the key ranges of each map; then the row's end, or, with keys split between CTAs, the scratch
+  for (int r = warp; r < T.rows_used; r += WARPS) {
+    const int tok = r / Gc, hd = r - tok * Gc;
+    if (hd >= T.nheads) continue;
+    float val[2][NC][2], mx[2], sum[2];
 #pragma unroll
-  for (int rr = 0; rr < 2; ++rr) {
-    l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 1);
-    l[rr] += __shfl_xor_sync(0xffffffffu, l[rr], 2);
-  }
-  const float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
-  if (map == 1 && warp_active) {
+    for (int mp = 0; mp < 2; ++mp)
+      merge_partials(part + ((size_t)(mp * 4 + (r >> 4) * KS) * 16 + (r & 15)) * PROW, (size_t)16 * PROW, KS, lane, val[mp], mx[mp], sum[mp]);
+    const size_t t = (size_t)(q0 + tok0 + tok);
+    if (p.splits <= 1) {
+      finish_row(p, val[0], val[1], sum[0], sum[1], t, head0 + hd, lane);
+    } else {
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      float* dst = sC + (rr ? r1 : r0) * (DV + 1);
+      for (int mp = 0; mp < 2; ++mp) {
+        float* dst = p.scratch + (((size_t)s * p.nh + head0 + hd) * p.splits + split) * 2 * SROW + mp * SROW;
 #pragma unroll
-      for (int j = 0; j < DV / 8; ++j) {
-        const int dim = j * 8 + (lane & 3) * 2;
-        dst[dim] = o[j][2 * rr] * inv[rr];
-        dst[dim + 1] = o[j][2 * rr + 1] * inv[rr];
+        for (int c = 0; c < NC; ++c) {
+          const int d = c * 64 + lane * 2;
+          if (d < DV) *reinterpret_cast<float2*>(dst + d) = make_float2(val[mp][c][0], val[mp][c][1]);
+        }
+        if (lane == 0) {
+          dst[DV] = mx[mp];
+          dst[DV + 1] = sum[mp];
+        }
       }
     }
   }
-  __syncthreads();
-  if (map == 0 && warp_active) {
+}
+
+// Keys split between CTAs: a warp per (sequence, head) merges the splits of each map and ends the row.
+__global__ void diff_merge_splits_kernel(const Params p, int num_seqs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= num_seqs * p.nh) return;
+  const int s = row / p.nh, head = row - s * p.nh;
+  float val[2][NC][2], mx[2], sum[2];
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      const int r = rr ? r1 : r0;
-      const float* other = sC + r * (DV + 1);
-      float ss = 0.f;
-#pragma unroll
-      for (int j = 0; j < DV / 8; ++j) {
-        const int dim = j * 8 + (lane & 3) * 2;
-        const float a = o[j][2 * rr] * inv[rr] - p.lambda * other[dim];
-        const float b = o[j][2 * rr + 1] * inv[rr] - p.lambda * other[dim + 1];
-        o[j][2 * rr] = a;
-        o[j][2 * rr + 1] = b;
-        ss = fmaf(a, a, fmaf(b, b, ss));
-      }
-      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-      if (!rvalid[rr]) continue;
-      const int tok = r / Gc, hd = r - tok * Gc;
-      const size_t t = (size_t)(q0 + tok0 + tok);
-      const float g = p.gate != nullptr ? 1.f / (1.f + expf(-__bfloat162float(p.gate[t * p.gate_stride + head0 + hd]))) : 1.f;
-      const float f = rsqrtf(ss / (float)DV + p.eps) * p.post * g;
-      bf16* dst = p.out + (t * p.nh + head0 + hd) * DV;
-#pragma unroll
-      for (int j = 0; j < DV / 8; ++j) {
-        const int dim = j * 8 + (lane & 3) * 2;
-        *reinterpret_cast<__nv_bfloat162*>(dst + dim) = __floats2bfloat162_rn(o[j][2 * rr] * f, o[j][2 * rr + 1] * f);
-      }
-    }
-  }
+  for (int mp = 0; mp < 2; ++mp) merge_partials(p.scratch + (size_t)row * p.splits * 2 * SROW + mp * SROW, (size_t)2 * SROW, p.splits, lane, val[mp], mx[mp], sum[mp]);
+  finish_row(p, val[0], val[1], sum[0], sum[1], (size_t)p.q_start[s], head, lane);
 }
 
 }  // namespace tc
@@ -520,13 +649,16 @@ __global__ void __launch_bounds__(THREADS) diff_attention_tc_kernel(const Params
 DLI_EXPORT int dli_diff_attention_tc(void* out, const void* q, const void* k_pool, const void* v_pool, const int* block_tables, int max_blocks,
                                      const int* q_start, const int* kv_len, int num_seqs, int max_q_len, const void* gate, int gate_stride,
                                      int nh, int nkv, int page_size, int window, int keep_first, float scale, float lambda, float post, float eps,
-                                     cudaStream_t stream) {
+                                     int splits, float* scratch, cudaStream_t stream) {
   using namespace tc;
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
+  if (splits > 1 && (max_q_len != 1 || scratch == nullptr || splits > 65535)) return DLI_ERR_UNSUPPORTED;
   static OncePerDevice attr;
   if (!attr.here()) {
     cudaError_t e = cudaFuncSetAttribute(diff_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(diff_attention_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return (int)e;
     attr.here() = true;
   }
@@ -540,9 +672,14 @@ DLI_EXPORT int dli_diff_attention_tc(void* out, const void* q, const void* k_poo
   p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
   p.tokens_per_tile = BLOCK_M / p.heads_per_chunk;
   p.scale_log2 = scale * 1.4426950408889634f; p.lambda = lambda; p.post = post; p.eps = eps;
-  const int tiles = (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
+  p.splits = splits > 1 ? splits : 1; p.scratch = scratch;
+  const int tiles = p.splits > 1 ? p.splits : (max_q_len + p.tokens_per_tile - 1) / p.tokens_per_tile;
   if (num_seqs > 65535 || nkv * p.head_chunks > 65535) return DLI_ERR_UNSUPPORTED;
   launch_pdl(diff_attention_tc_kernel, dim3(tiles, num_seqs, nkv * p.head_chunks), dim3(THREADS), SMEM_BYTES, stream, 1, p);
+  if (p.splits > 1) {
+    const int warps = 4;
+    launch_pdl(diff_merge_splits_kernel, dim3((num_seqs * nh + warps - 1) / warps), dim3(warps * 32), 0, stream, 1, p, num_seqs);
+  }
   return (int)cudaGetLastError();
 }
 #endif

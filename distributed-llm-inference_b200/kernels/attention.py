@@ -122,8 +122,15 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, cache, batch, gate: torch
     tokens; float32 and any other size: the CUDA-core kernel."""
     group = batch.group(cache.group)
     if out.dtype == torch.bfloat16 and ops.diff_attention_tc_supported(cache.k.shape[3] // 2, cache.v.shape[3]):
+        splits, scratch = 1, None
+        if batch.max_q_len == 1 and out.is_cuda:  # few single tokens: their key tiles are divided between CTAs to fill the GPU
+            nkv, vdim = cache.k.shape[1], cache.v.shape[3]
+            seen = min(batch.max_kv_len, window + keep_first + 64) if window else batch.max_kv_len
+            splits = choose_splits(batch.num_seqs, nkv * -(-(num_heads // nkv) // 64), seen, one_wave(2), fill_last_wave=False)
+            if splits > 1:
+                scratch = torch.empty(ops.diff_attention_scratch(batch.num_seqs, num_heads, vdim, splits), dtype=torch.float32, device=out.device)
         ops.diff_attention_tc(out, q, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, batch.num_seqs, batch.max_q_len, gate,
-                              num_heads, scale, window, keep_first, lam, post, eps)
+                              num_heads, scale, window, keep_first, lam, post, eps, splits, scratch)
         return
     ops.diff_attention_simt(out, q, cache.k, cache.v, group.block_tables, batch.seq_of_token, batch.positions, gate, num_heads, scale,
                             window, keep_first, lam, post, eps)

@@ -1325,16 +1325,21 @@ def diff_attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
 
 def diff_attention_tc_supported(dim: int, vdim: int) -> bool:
     """Sizes of a map's keys and of the values that the tensor-core kernel of differential attention takes (bfloat16)."""
-    fits = 64 * (12 * dim + 4 * vdim + 80) <= 227 * 1024  # 64 query rows and two stages of 64 key and value rows in shared memory
+    stages = 64 * (8 * dim + 4 * vdim + 64)  # two stages of 64 key and value rows; the warps' partial results take their place at the end
+    partial = 512 * (vdim + (8 if vdim % 32 == 0 else 24))
+    fits = 64 * (4 * dim + 16) + max(stages, partial) <= 227 * 1024  # and 64 query rows in front of them
     return dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 256 and 16 <= vdim <= 256 and fits
 
 
 def diff_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, num_seqs: int, max_q_len: int, gate: torch.Tensor | None, num_heads: int,
-                      scale: float, window: int | None, keep_first: int, lam: float, post: float, eps: float) -> None:
+                      scale: float, window: int | None, keep_first: int, lam: float, post: float, eps: float, splits: int = 1,
+                      scratch: torch.Tensor | None = None) -> None:
     """``diff_attention_simt`` on tensor cores (bfloat16; one library per pair of sizes): sequences given by their first rows
     ``q_start`` [seqs + 1] and lengths in the cache after this step ``kv_len`` [seqs]; prompt portions and single tokens in one
-    launch, sized for ``max_q_len`` rows a sequence."""
+    launch, sized for ``max_q_len`` rows a sequence.  ``splits`` > 1 (single tokens only): the key tiles of every sequence are
+    divided between that many CTAs, whose partial results meet in ``scratch`` (float32, ``diff_attention_scratch`` numbers)
+    and are merged by a second kernel."""
     _need(out, "out", torch.bfloat16), _need(q, "q", torch.bfloat16), _need(k_pool, "k_pool", torch.bfloat16), _need(v_pool, "v_pool", torch.bfloat16)
     n = q.shape[0]
     _, nkv, page_size, d2 = k_pool.shape
@@ -1346,9 +1351,22 @@ def diff_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, 
         if gate.dtype != out.dtype or gate.shape != (n, num_heads) or gate.stride(1) != 1 or not gate.is_cuda:
             raise KernelError("diff_attention_tc: gate must be [n, heads] with unit column stride")
         gate_stride = gate.stride(0)
+    splits = max(1, int(splits))
+    if splits > 1:
+        if max_q_len != 1:
+            raise KernelError("diff_attention_tc: keys are split between CTAs for single tokens only")
+        need = diff_attention_scratch(num_seqs, num_heads, vdim, splits)
+        if scratch is None or scratch.dtype != torch.float32 or not scratch.is_contiguous() or scratch.numel() < need or scratch.device != out.device:
+            raise KernelError(f"diff_attention_tc: {splits} splits need a float32 scratch of {need} numbers")
     f = _fn("diff_attention.cu", "dli_diff_attention_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
-                                                           c_void_p], defines={"DIFF_DK": d2 // 2, "DIFF_DV": vdim})
+                                                           c_int, c_void_p, c_void_p], defines={"DIFF_DK": d2 // 2, "DIFF_DV": vdim})
     _check(f(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1], _ptr(q_start), _ptr(kv_len), int(num_seqs),
              int(max_q_len), _ptr(gate), gate_stride, num_heads, nkv, page_size, int(window or 0), int(keep_first), float(scale), float(lam),
-             float(post), float(eps), _stream()), "diff_attention_tc")
+             float(post), float(eps), splits, _ptr(scratch) if splits > 1 else None, _stream()), "diff_attention_tc")
+
+
+def diff_attention_scratch(num_seqs: int, num_heads: int, vdim: int, splits: int) -> int:
+    """float32 numbers of the scratch in which ``splits`` CTAs leave a single token's partial results: for every sequence,
+    head, split and map the unnormalised outputs, their maximum and their sum."""
+    return num_seqs * num_heads * splits * 2 * (vdim + 2)

@@ -574,7 +574,7 @@ def diff_attention_simt(out, q, k_pool, v_pool, block_tables, seq_of_token, posi
 
 
 def diff_attention_tc(out, q, k_pool, v_pool, block_tables, q_start, kv_len, num_seqs, max_q_len, gate, num_heads, scale, window, keep_first, lam,
-                      post, eps):
+                      post, eps, splits=1, scratch=None):
     lens = (q_start[1:] - q_start[:-1]).long()
     seq = torch.repeat_interleave(torch.arange(num_seqs), lens)
     at = torch.arange(q.shape[0])

@@ -206,6 +206,43 @@ def test_diff_attention_kernels(dtype, nh, nkv, dim, vdim, rot, page, window, ke
     assert torch.allclose(out.float().cpu(), out_ref.float(), atol=1e-4 if dtype == torch.float32 else 6e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,dim,vdim,window,keep", [(8, 2, 64, 128, 100, 4), (2, 2, 32, 64, 0, 0), (3, 1, 48, 96, 70, 130), (12, 1, 16, 32, 65, 1)])
+def test_diff_attention_on_tensor_cores_over_many_key_tiles(nh, nkv, dim, vdim, window, keep):
+    """The tensor-core kernel against the CUDA-core kernel (bfloat16 both) where a row walks several tiles of keys: a long
+    portion, a short one behind a long context, single tokens at contexts on both sides of a tile's edge; row counts that
+    divide a map's warps by rows, by keys and both ways."""
+    from dli_b200.kernels import ops
+
+    page, dtype = 16, torch.bfloat16
+    q_lens, kv_lens = (150, 7, 1, 1, 1, 20), (150, 300, 257, 64, 65, 21)
+    S, n = len(q_lens), sum(q_lens)
+    per_seq = -(-max(kv_lens) // page)
+    order = torch.tensor(np.random.default_rng(1).permutation(S * per_seq), dtype=torch.int32).view(S, per_seq).cuda()
+    k_pool = _rand((S * per_seq, nkv, page, 2 * dim), dtype, 21)
+    v_pool = _rand((S * per_seq, nkv, page, vdim), dtype, 22)
+    q = _rand((n, nh * 2 * dim), dtype, 23) * 3.0
+    gate = _rand((n, nh), dtype, 24)
+    seq = torch.tensor(np.repeat(np.arange(S), q_lens), dtype=torch.int32).cuda()
+    pos = torch.tensor(np.concatenate([np.arange(k - c, k) for c, k in zip(q_lens, kv_lens)]), dtype=torch.int32).cuda()
+    q_start = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32).cuda()
+    kv = torch.tensor(kv_lens, dtype=torch.int32).cuda()
+    ref, out = torch.empty((n, nh * vdim), dtype=dtype, device="cuda"), torch.empty((n, nh * vdim), dtype=dtype, device="cuda")
+    ops.diff_attention_simt(ref, q, k_pool, v_pool, order, seq, pos, gate, nh, dim**-0.5, window or None, keep, 0.45, 0.7, 1e-5)
+    assert ops.diff_attention_tc_supported(dim, vdim)
+    ops.diff_attention_tc(out, q, k_pool, v_pool, order, q_start, kv, S, max(q_lens), gate, nh, dim**-0.5, window or None, keep, 0.45, 0.7, 1e-5)
+    assert not torch.isnan(out).any()
+    assert torch.allclose(out.float(), ref.float(), atol=4e-2, rtol=2e-2)
+    # single tokens alone, their key tiles divided between CTAs (more CTAs than the shortest context has tiles)
+    singles = [i for i, c in enumerate(q_lens) if c == 1]
+    rows = torch.tensor([int(q_start[i]) for i in singles]).cuda()
+    for splits in (2, 3, 7):
+        part = torch.full((len(singles), nh * vdim), float("nan"), dtype=dtype, device="cuda")
+        scratch = torch.full((ops.diff_attention_scratch(len(singles), nh, vdim, splits),), float("nan"), dtype=torch.float32, device="cuda")
+        ops.diff_attention_tc(part, q[rows].contiguous(), k_pool, v_pool, order[singles].contiguous(), torch.arange(len(singles) + 1, dtype=torch.int32).cuda(),
+                              kv[singles].contiguous(), len(singles), 1, gate[rows].contiguous(), nh, dim**-0.5, window or None, keep, 0.45, 0.7, 1e-5, splits, scratch)
+        assert torch.allclose(part.float(), out[rows].float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_bounded_gate_times_shifted_up_kernel(dtype):
     from dli_b200.kernels import ops
