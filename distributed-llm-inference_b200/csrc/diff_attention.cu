@@ -32,9 +32,17 @@ __global__ void diff_prep_kernel(T* __restrict__ q_out, const T* __restrict__ pr
                                  T* __restrict__ v_pool, int nh, int nkv, int dim, int vdim, int rot, int page_size) {
   pdl_launch_dependents();
   pdl_wait();
+  extern __shared__ float trig[];  // the token's cosines [rot / 2] and sines [rot / 2] times amp, shared by all heads and maps
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const float pos = (float)positions[t];
+  for (int j = threadIdx.x; 2 * j < rot; j += blockDim.x) {
+    float sn, cs;
+    sincosf(pos * freq[j], &sn, &cs);
+    trig[j] = cs * amp;
+    trig[rot / 2 + j] = sn * amp;
+  }
+  __syncthreads();
   const T* row = proj + (size_t)t * proj_stride;
   const bool writes = k_col >= 0;
   long long kbase = 0, vbase = 0;
@@ -68,10 +76,7 @@ __global__ void diff_prep_kernel(T* __restrict__ q_out, const T* __restrict__ pr
       float a = to_float(src[e0]) * rstd * w[e0];
       float b = e1 < dim ? to_float(src[e1]) * rstd * w[e1] : 0.f;
       if (e1 < rot) {
-        float sn, cs;
-        sincosf(pos * freq[j], &sn, &cs);
-        sn *= amp;
-        cs *= amp;
+        const float cs = trig[j], sn = trig[rot / 2 + j];
         const float ra = a * cs - b * sn, rb = b * cs + a * sn;
         a = ra;
         b = rb;
@@ -193,11 +198,13 @@ DLI_EXPORT int dli_diff_prep(void* q_out, const void* proj, int proj_stride, int
   if (rot % 2 || rot < 0 || rot > dim || nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
   const int units = 2 * nh + (k_col >= 0 ? 2 * nkv : 0);
   const int threads = 32 * (units < 8 ? units : 8);
+  const size_t smem = (size_t)rot * sizeof(float);
+  if (smem > 48 * 1024) return DLI_ERR_UNSUPPORTED;
   if (dtype == DLI_F32)
-    launch_pdl((diff_prep_kernel<float>), dim3(n), dim3(threads), 0, stream, 1, (float*)q_out, (const float*)proj, proj_stride, k_col, v_col, wq,
+    launch_pdl((diff_prep_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)q_out, (const float*)proj, proj_stride, k_col, v_col, wq,
                wk, eps, positions, freq, amp, slots, (float*)k_pool, (float*)v_pool, nh, nkv, dim, vdim, rot, page_size);
   else
-    launch_pdl((diff_prep_kernel<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, 1, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj,
+    launch_pdl((diff_prep_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj,
                proj_stride, k_col, v_col, wq, wk, eps, positions, freq, amp, slots, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, dim,
                vdim, rot, page_size);
   return (int)cudaGetLastError();
@@ -322,19 +329,24 @@ __device__ __forceinline__ void walk(const Params& p, const Tile& T, unsigned ch
   const bool warp_active = wrow < T.rows_used;
   const int Gc = T.Gc;
 
-  // four threads a key row: one look into the block table, then the row's 16-byte chunks in turn
-  auto load_tile = [&](int stage, int t) {
-    const int r = tid >> 2, key = t * BLOCK_N + r;
+  auto tile_index = [&](int it) { return it < T.kept_tiles ? it : T.first_tile + (it - T.kept_tiles); };
+  // Four threads a key row.  The row's page is looked up one tile ahead of its copies (locate), so that the block table's
+  // answer has arrived when the copies are issued: page < 0 is a row that no query of the tile sees (zeros, nothing read).
+  const int lrow = tid >> 2;
+  auto locate = [&](int it) -> int {
+    if (it >= T.it1) return -1;
+    const int key = tile_index(it) * BLOCK_N + lrow;
     const bool ok = key < T.hi && (key >= T.lo || key < T.kept);
-    size_t at = 0;
-    if (ok) {
-      const int blk = key / p.page_size;
-      at = ((size_t)T.table[blk] * p.nkv + T.kvh) * p.page_size + (key - blk * p.page_size);
-    }
+    return ok ? T.table[key / p.page_size] : -1;
+  };
+  auto load_tile = [&](int stage, int it, int page) {
+    const int key = tile_index(it) * BLOCK_N + lrow;
+    const bool ok = page >= 0;
+    const size_t at = ok ? ((size_t)page * p.nkv + T.kvh) * p.page_size + key % p.page_size : 0;
     const bf16* gK = p.k_pool + at * 2 * DK;
     const bf16* gV = p.v_pool + at * DV;
-    const uint32_t dK = smem_u32(sK + stage * KTILE + r * KROW), dV = smem_u32(sV + stage * VTILE + r * VROW);
-    const int bytes = ok ? 16 : 0;  // 0: the chunk is filled with zeros and nothing is read
+    const uint32_t dK = smem_u32(sK + stage * KTILE + lrow * KROW), dV = smem_u32(sV + stage * VTILE + lrow * VROW);
+    const int bytes = ok ? 16 : 0;
 #pragma unroll
     for (int i = 0; i < (KCHUNKS + VCHUNKS + 3) / 4; ++i) {
       const int c = (tid & 3) + 4 * i;
@@ -342,7 +354,6 @@ __device__ __forceinline__ void walk(const Params& p, const Tile& T, unsigned ch
       else if (c < KCHUNKS + VCHUNKS) cp_async16(dV + (c - KCHUNKS) * 16, gV + (c - KCHUNKS) * 8, bytes);
     }
   };
-  auto tile_index = [&](int it) { return it < T.kept_tiles ? it : T.first_tile + (it - T.kept_tiles); };
 
   const int r0 = wrow + (lane >> 2), r1 = r0 + 8;
   int rpos[2];
@@ -361,12 +372,14 @@ __device__ __forceinline__ void walk(const Params& p, const Tile& T, unsigned ch
 #pragma unroll
   for (int j = 0; j < DV / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  if (T.it0 < T.it1) load_tile(0, tile_index(T.it0));
+  if (T.it0 < T.it1) load_tile(0, T.it0, locate(T.it0));
   cp_async_commit();
+  int page_next = locate(T.it0 + 1);
   for (int it = T.it0; it < T.it1; ++it) {
     const int stage = (it - T.it0) & 1;
-    if (it + 1 < T.it1) load_tile(stage ^ 1, tile_index(it + 1));
+    if (it + 1 < T.it1) load_tile(stage ^ 1, it + 1, page_next);
     cp_async_commit();
+    page_next = locate(it + 2);
     cp_async_wait<1>();
     __syncthreads();
     if (warp_active) {

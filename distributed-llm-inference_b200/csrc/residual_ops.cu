@@ -62,18 +62,57 @@ __global__ void pair_embedding_kernel(float* __restrict__ h, const T* __restrict
 }
 
 // ---------------------------------------------------------------- RMS norm in groups
-// 1 / sqrt(mean(v^2) + eps) of each of `groups` equal consecutive parts of a row, left in rstd[] (shared).
-template <typename Load>
-__device__ __forceinline__ void group_rstd(Load load, int H, int groups, float eps, float* rstd, float* red) {
+// Four consecutive numbers of a row at once (the callers take this path when the row and a group are multiples of four
+// long, so a vector starts on its own size's boundary and lies in one group).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// 1 / sqrt(mean(v^2) + eps) of each of `groups` equal consecutive parts of a row, left in rstd[] (shared).  The warps
+// divide the groups between them, several warps to a group where there are fewer groups than warps; which numbers a lane
+// adds, and in which order the lanes' and warps' sums meet, is fixed by the sizes alone.
+template <typename T>
+__device__ __forceinline__ void group_rstd(const T* row, int H, int groups, float eps, bool vec, float* rstd, float* partial /* >= groups * warps */) {
   const int gs = H / groups;
-  for (int g = 0; g < groups; ++g) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int per = warps / groups > 1 ? warps / groups : 1;  // warps to a group
+  int len = (gs + per - 1) / per;  // numbers of a group that one warp adds
+  if (vec) len = (len + 3) & ~3;
+  for (int ch = warp; ch < groups * per; ch += warps) {
+    const int g = ch / per, part = ch - g * per;
+    const int first = part * len, last = min(gs, first + len);
+    const T* src = row + (size_t)g * gs;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < gs; c += blockDim.x) {
-      const float v = load(g * gs + c);
-      ss = fmaf(v, v, ss);
+    if (vec) {
+      for (int c = first + lane * 4; c < last; c += 128) {
+        const float4 v = load4(src + c);
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+      }
+    } else {
+      for (int c = first + lane; c < last; c += 32) {
+        const float v = to_float(src[c]);
+        ss = fmaf(v, v, ss);
+      }
     }
-    ss = block_sum(ss, red);
-    if (threadIdx.x == 0) rstd[g] = rsqrtf(ss / (float)gs + eps);
+    ss = warp_sum(ss);
+    if (lane == 0) partial[ch] = ss;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g < groups; g += blockDim.x) {
+    float ss = 0.f;
+    for (int i = 0; i < per; ++i) ss += partial[g * per + i];
+    rstd[g] = rsqrtf(ss / (float)gs + eps);
   }
   __syncthreads();
 }
@@ -81,17 +120,31 @@ __device__ __forceinline__ void group_rstd(Load load, int H, int groups, float e
 // h += mult * norm(a) * w; y = h in the activation dtype (if y).  TA: dtype of a and y.
 template <typename TA>
 __global__ void group_norm_add_kernel(float* __restrict__ h, const TA* __restrict__ a, const float* __restrict__ w, int groups, float eps,
-                                      float mult, TA* __restrict__ y, int H) {
+                                      float mult, TA* __restrict__ y, int H, int vec) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float red[33];
+  __shared__ float partial[MAX_GROUPS * (THREADS / 32)];
   __shared__ float rstd[MAX_GROUPS];
   const size_t row = (size_t)blockIdx.x * H;
   const TA* ar = a + row;
-  group_rstd([&](int c) { return to_float(ar[c]); }, H, groups, eps, rstd, red);
+  group_rstd(ar, H, groups, eps, vec != 0, rstd, partial);
   const int gs = H / groups;
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+      const float4 av = load4(ar + c), wv = load4(w + c);
+      float4 hv = load4(h + row + c);
+      const float f = mult * rstd[c / gs];
+      hv.x += f * (av.x * wv.x);
+      hv.y += f * (av.y * wv.y);
+      hv.z += f * (av.z * wv.z);
+      hv.w += f * (av.w * wv.w);
+      store4(h + row + c, hv);
+      if (y != nullptr) store4(y + row + c, hv);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    const float v = h[row + c] + mult * (to_float(ar[c]) * rstd[c / gs] * w[c]);
+    const float v = h[row + c] + mult * rstd[c / gs] * (to_float(ar[c]) * w[c]);
     h[row + c] = v;
     if (y != nullptr) y[row + c] = from_float<TA>(v);
   }
@@ -100,13 +153,13 @@ __global__ void group_norm_add_kernel(float* __restrict__ h, const TA* __restric
 // y[i] = norm(h[rows[i]]) * w  (rows == nullptr: row i)
 template <typename TY>
 __global__ void group_norm_rows_kernel(TY* __restrict__ y, const float* __restrict__ h, const float* __restrict__ w, const int* __restrict__ rows,
-                                       int groups, float eps, int H) {
+                                       int groups, float eps, int H, int vec) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float red[33];
+  __shared__ float partial[MAX_GROUPS * (THREADS / 32)];
   __shared__ float rstd[MAX_GROUPS];
   const float* hr = h + (size_t)(rows != nullptr ? rows[blockIdx.x] : blockIdx.x) * H;
-  group_rstd([&](int c) { return hr[c]; }, H, groups, eps, rstd, red);
+  group_rstd(hr, H, groups, eps, vec != 0, rstd, partial);
   const int gs = H / groups;
   for (int c = threadIdx.x; c < H; c += blockDim.x) y[(size_t)blockIdx.x * H + c] = from_float<TY>(hr[c] * rstd[c / gs] * w[c]);
 }
@@ -140,6 +193,12 @@ __global__ void depth_average_kernel(float* __restrict__ out, const float* __res
   }
 }
 
+// Rows and groups that are multiples of four numbers long, on pointers that let four numbers be read at once.
+inline int vector_rows(int H, int groups, const void* h, const void* w, const void* a, const void* y) {
+  const uintptr_t all = (uintptr_t)h | (uintptr_t)w | (uintptr_t)a | (uintptr_t)y;
+  return H % 4 == 0 && (H / groups) % 4 == 0 && all % 16 == 0;
+}
+
 inline int grid_for(long long total) {
   const long long want = (total + THREADS - 1) / THREADS, most = (long long)sm_count() * 16;
   return (int)(want < most ? (want > 0 ? want : 1) : most);
@@ -166,11 +225,12 @@ DLI_EXPORT int dli_group_norm_add(float* h, const void* a, const float* w, int g
                                   cudaStream_t stream) {
   if (n == 0) return 0;
   if (groups < 1 || groups > MAX_GROUPS || H % groups) return DLI_ERR_UNSUPPORTED;
+  const int vec = vector_rows(H, groups, h, w, a, y);
   if (dtype == DLI_F32)
-    launch_pdl((group_norm_add_kernel<float>), dim3(n), dim3(THREADS), 0, stream, 1, h, (const float*)a, w, groups, eps, mult, (float*)y, H);
+    launch_pdl((group_norm_add_kernel<float>), dim3(n), dim3(THREADS), 0, stream, 1, h, (const float*)a, w, groups, eps, mult, (float*)y, H, vec);
   else
     launch_pdl((group_norm_add_kernel<__nv_bfloat16>), dim3(n), dim3(THREADS), 0, stream, 1, h, (const __nv_bfloat16*)a, w, groups, eps, mult,
-               (__nv_bfloat16*)y, H);
+               (__nv_bfloat16*)y, H, vec);
   return (int)cudaGetLastError();
 }
 
@@ -178,10 +238,11 @@ DLI_EXPORT int dli_group_norm_rows(void* y, const float* h, const float* w, cons
                                    cudaStream_t stream) {
   if (n == 0) return 0;
   if (groups < 1 || groups > MAX_GROUPS || H % groups) return DLI_ERR_UNSUPPORTED;
+  const int vec = vector_rows(H, groups, h, w, nullptr, nullptr);
   if (dtype == DLI_F32)
-    launch_pdl((group_norm_rows_kernel<float>), dim3(n), dim3(THREADS), 0, stream, 1, (float*)y, h, w, rows, groups, eps, H);
+    launch_pdl((group_norm_rows_kernel<float>), dim3(n), dim3(THREADS), 0, stream, 1, (float*)y, h, w, rows, groups, eps, H, vec);
   else
-    launch_pdl((group_norm_rows_kernel<__nv_bfloat16>), dim3(n), dim3(THREADS), 0, stream, 1, (__nv_bfloat16*)y, h, w, rows, groups, eps, H);
+    launch_pdl((group_norm_rows_kernel<__nv_bfloat16>), dim3(n), dim3(THREADS), 0, stream, 1, (__nv_bfloat16*)y, h, w, rows, groups, eps, H, vec);
   return (int)cudaGetLastError();
 }
 
