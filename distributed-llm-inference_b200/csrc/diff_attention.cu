@@ -25,11 +25,18 @@ namespace {
 // ---------------------------------------------------------------- prep
 // proj row: q heads [nh][2][dim] from column 0; k heads [nkv][2][dim] from k_col; v [nkv][vdim] from v_col (k_col < 0: the
 // layer reads another layer's keys and values and writes none).
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void store2(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+
+// pairs != 0: every size and column is even, dim <= 256 and the pointers allow it, so a lane reads the two numbers that
+// rotate together at once and keeps them from the norm's sum to the rotation.
 template <typename T>
 __global__ void diff_prep_kernel(T* __restrict__ q_out, const T* __restrict__ proj, int proj_stride, int k_col, int v_col,
                                  const float* __restrict__ wq, const float* __restrict__ wk, float eps, const int* __restrict__ positions,
                                  const float* __restrict__ freq, float amp, const int* __restrict__ slots, T* __restrict__ k_pool,
-                                 T* __restrict__ v_pool, int nh, int nkv, int dim, int vdim, int rot, int page_size) {
+                                 T* __restrict__ v_pool, int nh, int nkv, int dim, int vdim, int rot, int page_size, int pairs) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float trig[];  // the token's cosines [rot / 2] and sines [rot / 2] times amp, shared by all heads and maps
@@ -42,7 +49,7 @@ __global__ void diff_prep_kernel(T* __restrict__ q_out, const T* __restrict__ pr
     trig[j] = cs * amp;
     trig[rot / 2 + j] = sn * amp;
   }
-  __syncthreads();
+  bool trig_ready = false;  // every warp has at least one unit: it meets the others behind its first unit's loads
   const T* row = proj + (size_t)t * proj_stride;
   const bool writes = k_col >= 0;
   long long kbase = 0, vbase = 0;
@@ -66,11 +73,47 @@ __global__ void diff_prep_kernel(T* __restrict__ q_out, const T* __restrict__ pr
       dst = k_pool + kbase + (long long)g * page_size * 2 * dim + m * dim;
     }
     float ss = 0.f;
+    if (pairs) {
+      float2 x[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = lane + 32 * i;
+        if (2 * j < dim) {
+          x[i] = load2(src + 2 * j);
+          ss = fmaf(x[i].x, x[i].x, fmaf(x[i].y, x[i].y, ss));
+        }
+      }
+      const float rstd = rsqrtf(warp_sum(ss) / (float)dim + eps);
+      if (!trig_ready) {
+        __syncthreads();
+        trig_ready = true;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = lane + 32 * i;
+        if (2 * j < dim) {
+          const float2 w2 = load2(w + 2 * j);
+          float a = x[i].x * rstd * w2.x, b = x[i].y * rstd * w2.y;
+          if (2 * j + 1 < rot) {
+            const float cs = trig[j], sn = trig[rot / 2 + j];
+            const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+            a = ra;
+            b = rb;
+          }
+          store2(dst + 2 * j, make_float2(a, b));
+        }
+      }
+      continue;
+    }
     for (int e = lane; e < dim; e += 32) {
       const float v = to_float(src[e]);
       ss = fmaf(v, v, ss);
     }
     const float rstd = rsqrtf(warp_sum(ss) / (float)dim + eps);
+    if (!trig_ready) {
+      __syncthreads();
+      trig_ready = true;
+    }
     for (int j = lane; 2 * j < dim; j += 32) {
       const int e0 = 2 * j, e1 = e0 + 1;
       float a = to_float(src[e0]) * rstd * w[e0];
@@ -85,7 +128,12 @@ __global__ void diff_prep_kernel(T* __restrict__ q_out, const T* __restrict__ pr
       if (e1 < dim) dst[e1] = from_float<T>(b);
     }
   }
-  if (writes) {
+  if (writes && pairs) {
+    for (int i = 2 * threadIdx.x; i < nkv * vdim; i += 2 * blockDim.x) {
+      const int g = i / vdim, e = i - g * vdim;
+      store2(v_pool + vbase + (long long)g * page_size * vdim + e, load2(row + v_col + i));  // float32 both ways, or bfloat16 unchanged
+    }
+  } else if (writes) {
     for (int i = threadIdx.x; i < nkv * vdim; i += blockDim.x) {
       const int g = i / vdim, e = i - g * vdim;
       v_pool[vbase + (long long)g * page_size * vdim + e] = row[v_col + i];
@@ -200,13 +248,15 @@ DLI_EXPORT int dli_diff_prep(void* q_out, const void* proj, int proj_stride, int
   const int threads = 32 * (units < 8 ? units : 8);
   const size_t smem = (size_t)rot * sizeof(float);
   if (smem > 48 * 1024) return DLI_ERR_UNSUPPORTED;
+  const uintptr_t ptrs = (uintptr_t)q_out | (uintptr_t)proj | (uintptr_t)wq | (uintptr_t)wk | (uintptr_t)k_pool | (uintptr_t)v_pool;
+  const int pairs = dim % 2 == 0 && dim <= 256 && vdim % 2 == 0 && proj_stride % 2 == 0 && (k_col < 0 || (k_col % 2 == 0 && v_col % 2 == 0)) && ptrs % 8 == 0;
   if (dtype == DLI_F32)
     launch_pdl((diff_prep_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)q_out, (const float*)proj, proj_stride, k_col, v_col, wq,
-               wk, eps, positions, freq, amp, slots, (float*)k_pool, (float*)v_pool, nh, nkv, dim, vdim, rot, page_size);
+               wk, eps, positions, freq, amp, slots, (float*)k_pool, (float*)v_pool, nh, nkv, dim, vdim, rot, page_size, pairs);
   else
     launch_pdl((diff_prep_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)proj,
                proj_stride, k_col, v_col, wq, wk, eps, positions, freq, amp, slots, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, dim,
-               vdim, rot, page_size);
+               vdim, rot, page_size, pairs);
   return (int)cudaGetLastError();
 }
 
