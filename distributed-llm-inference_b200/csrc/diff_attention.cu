@@ -554,17 +554,36 @@ constexpr int SROW = DV + 2;         // floats of one map's partial result in th
 
 // A warp merges `count` partial results of one row and map, `stride` floats apart, each DV unnormalised outputs followed by
 // its maximum (in units of log2) and its sum: the merged outputs (still unnormalised), their maximum and sum.
+// MANY: the partial results are many and far (the scratch of split keys): maxima and sums are read a partial result a
+// lane, so that their loads are in flight together; else (a CTA's own few, in shared memory) every lane reads them all.
+template <bool MANY>
 __device__ __forceinline__ void merge_partials(const float* src, size_t stride, int count, int lane, float (&val)[NC][2], float& mx, float& sum) {
-  mx = -CUDART_INF_F;
-  for (int i = 0; i < count; ++i) mx = fmaxf(mx, src[i * stride + DV]);
-  sum = 0.f;
+  if (MANY) {
+    float m_lane = -CUDART_INF_F;
+    for (int i = lane; i < count; i += 32) m_lane = fmaxf(m_lane, src[i * stride + DV]);
+    mx = warp_max(m_lane);
+    float s_lane = 0.f;
+    for (int i = lane; i < count; i += 32) {
+      const float mi = src[i * stride + DV];
+      s_lane = fmaf(mi == -CUDART_INF_F ? 0.f : exp2f(mi - mx), src[i * stride + DV + 1], s_lane);
+    }
+    sum = warp_sum(s_lane);
+  } else {
+    mx = -CUDART_INF_F;
+    for (int i = 0; i < count; ++i) mx = fmaxf(mx, src[i * stride + DV]);
+    sum = 0.f;
+    for (int i = 0; i < count; ++i) {
+      const float mi = src[i * stride + DV];
+      sum = fmaf(mi == -CUDART_INF_F ? 0.f : exp2f(mi - mx), src[i * stride + DV + 1], sum);
+    }
+  }
 #pragma unroll
   for (int c = 0; c < NC; ++c) val[c][0] = val[c][1] = 0.f;
+#pragma unroll 4
   for (int i = 0; i < count; ++i) {
     const float* pr = src + i * stride;
     const float mi = pr[DV];
     const float f = mi == -CUDART_INF_F ? 0.f : exp2f(mi - mx);  // a key range in which the row saw nothing
-    sum = fmaf(f, pr[DV + 1], sum);
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
       const int d = c * 64 + lane * 2;
@@ -671,7 +690,7 @@ __global__ void __launch_bounds__(THREADS, MIN_CTAS) diff_attention_tc_kernel(co
     float val[2][NC][2], mx[2], sum[2];
 #pragma unroll
     for (int mp = 0; mp < 2; ++mp)
-      merge_partials(part + ((size_t)(mp * 4 + (r >> 4) * KS) * 16 + (r & 15)) * PROW, (size_t)16 * PROW, KS, lane, val[mp], mx[mp], sum[mp]);
+      merge_partials<false>(part + ((size_t)(mp * 4 + (r >> 4) * KS) * 16 + (r & 15)) * PROW, (size_t)16 * PROW, KS, lane, val[mp], mx[mp], sum[mp]);
     const size_t t = (size_t)(q0 + tok0 + tok);
     if (p.splits <= 1) {
       finish_row(p, val[0], val[1], sum[0], sum[1], t, head0 + hd, lane);
@@ -703,7 +722,7 @@ __global__ void diff_merge_splits_kernel(const Params p, int num_seqs) {
   const int s = row / p.nh, head = row - s * p.nh;
   float val[2][NC][2], mx[2], sum[2];
 #pragma unroll
-  for (int mp = 0; mp < 2; ++mp) merge_partials(p.scratch + (size_t)row * p.splits * 2 * SROW + mp * SROW, (size_t)2 * SROW, p.splits, lane, val[mp], mx[mp], sum[mp]);
+  for (int mp = 0; mp < 2; ++mp) merge_partials<true>(p.scratch + (size_t)row * p.splits * 2 * SROW + mp * SROW, (size_t)2 * SROW, p.splits, lane, val[mp], mx[mp], sum[mp]);
   finish_row(p, val[0], val[1], sum[0], sum[1], (size_t)p.q_start[s], head, lane);
 }
 

@@ -43,14 +43,15 @@ CLUSTER_SPLITS_MAX = ops.DECODE_TMA_CLUSTER_SPLITS  # splits that the TMA decode
 CLUSTER_16_MAX_CTAS_PER_SPLIT = 16
 
 
-def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int | None = None, fill_last_wave: bool = True) -> int:
+def choose_splits(num_seqs: int, ctas_per_seq: int, max_kv_len: int, wave: int | None = None, fill_last_wave: bool = True,
+                  min_tiles: int | None = None) -> int:
     """Key splits for single-token sequences: as many as still fit the GPU in one wave (a second,
     partly filled wave costs more than the extra parallelism brings), none shorter than
     MIN_TILES_PER_SPLIT key tiles (the role of src/dli/model/paged_attention.py:63-74)."""
     wave = one_wave(2) if wave is None else wave
     pairs = max(1, num_seqs * ctas_per_seq)
     tiles = -(-max_kv_len // 64)
-    most = max(1, tiles // MIN_TILES_PER_SPLIT)
+    most = max(1, tiles // (min_tiles or MIN_TILES_PER_SPLIT))
     if pairs <= wave:
         return max(1, min(wave // pairs, most))
     if not fill_last_wave:
@@ -126,7 +127,8 @@ def diff_attention(out: torch.Tensor, q: torch.Tensor, cache, batch, gate: torch
         if batch.max_q_len == 1 and out.is_cuda:  # few single tokens: their key tiles are divided between CTAs to fill the GPU
             nkv, vdim = cache.k.shape[1], cache.v.shape[3]
             seen = min(batch.max_kv_len, window + keep_first + 64) if window else batch.max_kv_len
-            splits = choose_splits(batch.num_seqs, nkv * -(-(num_heads // nkv) // 64), seen, one_wave(2), fill_last_wave=False)
+            wave = one_wave(ops.diff_attention_tc_ctas_per_sm(cache.k.shape[3] // 2, vdim))
+            splits = choose_splits(batch.num_seqs, nkv * -(-(num_heads // nkv) // 64), seen, wave, fill_last_wave=False, min_tiles=1)
             if splits > 1:
                 scratch = torch.empty(ops.diff_attention_scratch(batch.num_seqs, num_heads, vdim, splits), dtype=torch.float32, device=out.device)
         ops.diff_attention_tc(out, q, cache.k, cache.v, group.block_tables, batch.q_start, batch.kv_len, batch.num_seqs, batch.max_q_len, gate,

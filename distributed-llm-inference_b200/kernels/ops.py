@@ -1323,12 +1323,21 @@ def diff_attention_simt(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
              float(post), float(eps), DT_CODE[out.dtype], _stream()), "diff_attention_simt")
 
 
-def diff_attention_tc_supported(dim: int, vdim: int) -> bool:
-    """Sizes of a map's keys and of the values that the tensor-core kernel of differential attention takes (bfloat16)."""
+def _diff_attention_tc_smem(dim: int, vdim: int) -> int:
     stages = 64 * (8 * dim + 4 * vdim + 64)  # two stages of 64 key and value rows; the warps' partial results take their place at the end
     partial = 512 * (vdim + (8 if vdim % 32 == 0 else 24))
-    fits = 64 * (4 * dim + 16) + max(stages, partial) <= 227 * 1024  # and 64 query rows in front of them
-    return dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 256 and 16 <= vdim <= 256 and fits
+    return 64 * (4 * dim + 16) + max(stages, partial)  # and 64 query rows in front of them
+
+
+def diff_attention_tc_supported(dim: int, vdim: int) -> bool:
+    """Sizes of a map's keys and of the values that the tensor-core kernel of differential attention takes (bfloat16)."""
+    return dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 256 and 16 <= vdim <= 256 and _diff_attention_tc_smem(dim, vdim) <= 227 * 1024
+
+
+def diff_attention_tc_ctas_per_sm(dim: int, vdim: int) -> int:
+    """CTAs of the tensor-core kernel that an SM holds at once (the kernel's own rule: two where 128 registers a thread and
+    half the shared memory suffice)."""
+    return 2 if dim <= 128 and vdim <= 128 and 2 * _diff_attention_tc_smem(dim, vdim) + 2048 <= 227 * 1024 else 1
 
 
 def diff_attention_tc(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
