@@ -697,8 +697,8 @@ def pokadra_sizes(width, heads, kv_heads, dim, window, gru, ff, pz, vocab=32000)
 
     def att(kv_from=None):
         m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": 2 * dim, "scale": dim**-0.5, "diff": 0.8,
-             "mask": {"size": window, "keep_first": 4},
-             "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+             "mask": {"size": window, "keep_first": 16},
+             "rot": {"base": 1000000.0, "dims": dim, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
         if kv_from is not None:
             m["kv_from"] = kv_from
         return {"type": "attention", "mlp": mlp(), "mixer": m}
@@ -706,8 +706,8 @@ def pokadra_sizes(width, heads, kv_heads, dim, window, gru, ff, pz, vocab=32000)
     def rec():
         return {"type": "mingru", "mlp": mlp(), "mixer": {"width": gru}}
 
-    pk = {"architecture": "Pokadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4}, "residual_mult": 0.5,
-          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "token_side": {"dim": 64},
+    pk = {"architecture": "Pokadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4}, "residual_mult": 0.4,
+          "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}}, "token_side": {"dim": 64},
           "layers": [att(), rec(), att(), rec(), att(kv_from=2), rec(), att(), rec()]}
     pazenex, _ = pazenex_sizes(width=width, heads=2 * heads, kv_heads=2 * kv_heads, dim=dim, ff=ff, vocab=vocab, **pz)
     for layer in pazenex["layers"]:
@@ -798,7 +798,7 @@ def pokadra_kernels(size, pk, tokens=4096, seqs=64):
         proj = torch.randn(n, cols, device=dev).to(bf)
         q = torch.empty(n, nh * 2 * d, dtype=bf, device=dev)
         wn = torch.ones(d, device=dev)
-        freq = (1.0 / (500000.0 ** (torch.arange(0, d, 2).float() / d))).to(dev)
+        freq = (1.0 / (1000000.0 ** (torch.arange(0, d, 2).float() / d))).to(dev)
         moved = n * ((nh * 2 * d + nkv * (2 * d + dv)) * 4)
         record(f"{label}.diff_prep", time_kernel(lambda: ops.diff_prep(q, proj, nh * 2 * d, nh * 2 * d + nkv * 2 * d, wn, wn, 1e-6, positions, freq, 1.2, slots,
                                                                         kp, vp, nh, nkv, d, dv, d, page)), moved, "qk_norm_rotary_store")
@@ -810,10 +810,11 @@ def pokadra_kernels(size, pk, tokens=4096, seqs=64):
                                                                                               values_from_keys=False)),
                n * (ph + 2 * pkv) * d * 4)
         att = torch.empty(n, nh * dv, dtype=bf, device=dev)
+        keep = 16  # first tokens of a sequence that every window keeps
         gate = proj[:, cols - nh :]
-        seen = sum(min(p + 1, window + 4) for p in range(context)) if S == 1 else float(min(context, window + 4))  # keys a token attends to
-        kv_read = S * min(context, window + 4 + (q_len if S == 1 else 0)) * nkv * (2 * d + dv) * 2
-        us = time_kernel(lambda: attn.diff_attention(att, q, LayerCache(0, kp, vp, page), batch, gate, nh, d**-0.5, window, 4, 0.5, 0.2, 1e-6))
+        seen = sum(min(p + 1, window + keep) for p in range(context)) if S == 1 else float(min(context, window + keep))  # keys a token attends to
+        kv_read = S * min(context, window + keep + (q_len if S == 1 else 0)) * nkv * (2 * d + dv) * 2
+        us = time_kernel(lambda: attn.diff_attention(att, q, LayerCache(0, kp, vp, page), batch, gate, nh, d**-0.5, window, keep, 0.5, 0.2, 1e-6))
         record(f"{label}.diff_attention", us, kv_read + n * nh * (2 * d + dv) * 2, "sink_attention", flops=S * seen * nh * (4.0 * d + 4.0 * dv))
         pq, po = torch.randn(n, ph * d, device=dev).to(bf), torch.empty(n, ph * d, dtype=bf, device=dev)
         us = time_kernel(lambda: attn.paged_attention(po, pq, LayerCache(0, kp2, vp2, page), batch, ph, d**-0.5, window, sink=0.0))
