@@ -13,6 +13,7 @@ from pathlib import Path
 from typing import Any, Callable
 
 from .llama import LlamaConfig, UnsupportedModelError, llama_model_spec
+from .lokolorn import LokolornConfig, lokolorn_model_spec
 from .pazenex import PazenexConfig, pazenex_model_spec
 from .pokadra import PokadraConfig, pokadra_model_spec
 from .spec import ModelSpec
@@ -64,3 +65,4 @@ register_architecture(
 register_architecture(Architecture("Pazenex", PazenexConfig.from_dict, pazenex_model_spec))
 register_architecture(Architecture("Sugonex", SugonexConfig.from_dict, sugonex_model_spec))
 register_architecture(Architecture("Pokadra", PokadraConfig.from_dict, pokadra_model_spec))
+register_architecture(Architecture("Lokolorn", LokolornConfig.from_dict, lokolorn_model_spec))

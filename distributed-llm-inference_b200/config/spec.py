@@ -23,11 +23,13 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (how the parts are wired, e.g. ``prenorm``)
-    and the parts by role (``mixer_norm``, ``mixer``, ``ffn_norm``, ``ffn``)."""
+    """One layer: an arrangement (how the parts are wired, e.g. ``prenorm``),
+    the parts by role (``mixer_norm``, ``mixer``, ``ffn_norm``, ``ffn``), and what the
+    arrangement itself needs (names of tensors of its own, sizes)."""
 
     arrangement: str
     parts: Mapping[str, PartSpec]
+    params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -57,6 +57,7 @@ struct Params {
   int nh, nkv, page_size, window;
   float scale_log2;          // softmax scale times log2(e)
   float sink_log2;           // score of a sink (a term of the denominator without a value) times log2(e); -inf: none
+  const float* sink_heads;   // if not null: a sink score per query head (natural units), instead of sink_log2
   int tokens_per_tile, heads_per_chunk, head_chunks, splits;
   float* part_acc;           // [n * nh, splits, D]   (splits > 1)
   float* part_ml;            // [n * nh, splits, 2]
@@ -67,6 +68,10 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 // What the sink adds to a denominator kept in units of 2^m.
 __device__ __forceinline__ float sink_term(float sink_log2, float m) {
   return sink_log2 == -CUDART_INF_F ? 0.f : exp2f(sink_log2 - m);
+}
+// The sink score of a query head, in log2 units.
+__device__ __forceinline__ float sink_of(const float* sink_heads, float sink_log2, int head) {
+  return sink_heads ? sink_heads[head] * 1.4426950408889634f : sink_log2;
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
@@ -324,7 +329,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Para
     const int tok = r / Gc, hd = r - tok * Gc;
     const size_t row = (size_t)(q0 + tok0 + tok) * p.nh + head0 + hd;  // (token, head) row of the batch
     if (p.splits == 1) {
-      const float inv = 1.f / (l[rr] + sink_term(p.sink_log2, m[rr]));
+      const float inv = 1.f / (l[rr] + sink_term(sink_of(p.sink_heads, p.sink_log2, head0 + hd), m[rr]));
       bf16* dst = p.out + row * D;
 #pragma unroll
       for (int j = 0; j < D / 8; ++j) {
@@ -479,7 +484,7 @@ __global__ void __launch_bounds__(THREADS) paged_decode_mma_kernel(const Params 
     }
     const size_t row = (size_t)token * p.nh + head0 + r;
     if (p.splits == 1) {
-      p.out[row * D + dcol] = __float2bfloat16_rn(acc / (L + sink_term(p.sink_log2, mx)));
+      p.out[row * D + dcol] = __float2bfloat16_rn(acc / (L + sink_term(sink_of(p.sink_heads, p.sink_log2, head0 + r), mx)));
     } else {
       p.part_acc[(row * p.splits + split) * D + dcol] = acc;
       if (dcol == 0) {
@@ -492,7 +497,8 @@ __global__ void __launch_bounds__(THREADS) paged_decode_mma_kernel(const Params 
 
 // out[row] = sum_i acc_i 2^(m_i - max m) / sum_i l_i 2^(m_i - max m); one block per (token, head) row.
 __global__ void merge_splits_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc,
-                                    const float* __restrict__ part_ml, int row0, int splits, float sink_log2) {
+                                    const float* __restrict__ part_ml, int row0, int splits, float sink_log2,
+                                    const float* __restrict__ sink_heads, int nh) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = (size_t)row0 + blockIdx.x;
@@ -504,7 +510,7 @@ __global__ void merge_splits_kernel(bf16* __restrict__ out, const float* __restr
     const float mi = ml[2 * i];
     if (mi != -CUDART_INF_F) L += ml[2 * i + 1] * exp2f(mi - mmax);
   }
-  L += sink_term(sink_log2, mmax);
+  L += sink_term(sink_of(sink_heads, sink_log2, (int)(row % nh)), mmax);
   const float inv = 1.f / L;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f;
@@ -525,8 +531,8 @@ __global__ void merge_splits_kernel(bf16* __restrict__ out, const float* __restr
 DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                        const int* block_tables, int max_blocks, const int* q_start, const int* kv_len,
                                        int seq0, int num_seqs, int max_q_len, int first_row, int nh, int nkv, int page_size,
-                                       int window, float scale, float sink, int splits, float* part_acc, float* part_ml,
-                                       cudaStream_t stream) {
+                                       int window, float scale, float sink, const float* sink_heads, int splits, float* part_acc,
+                                       float* part_ml, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (nkv < 1 || nh % nkv || splits < 1 || (splits > 1 && (max_q_len != 1 || !part_acc || !part_ml))) return DLI_ERR_UNSUPPORTED;
   static OncePerDevice configured;
@@ -552,6 +558,7 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
   p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sink_log2 = sink * 1.4426950408889634f;  // -inf (no sink) stays -inf
+  p.sink_heads = sink_heads;
   const int G = nh / nkv;
   p.heads_per_chunk = G < BLOCK_M ? G : BLOCK_M;
   p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
@@ -580,7 +587,7 @@ DLI_EXPORT int dli_paged_attention_mma(void* out, const void* q, long long q_str
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (splits > 1) {
-    launch_pdl((merge_splits_kernel), dim3(num_seqs * nh), dim3(D < 128 ? 64 : 128), 0, stream, 1, (bf16*)out, part_acc, part_ml, first_row * nh, splits, p.sink_log2);
+    launch_pdl((merge_splits_kernel), dim3(num_seqs * nh), dim3(D < 128 ? 64 : 128), 0, stream, 1, (bf16*)out, part_acc, part_ml, first_row * nh, splits, p.sink_log2, sink_heads, nh);
     e = cudaGetLastError();
   }
   return (int)e;
@@ -626,5 +633,5 @@ DLI_EXPORT int dli_paged_decode_attention_noalloc(void* out, const void* q, long
   float* part_ml = part_acc + rows * (unsigned long long)splits * (unsigned long long)D;
   if (splits == 1) part_acc = part_ml = nullptr;  // no partial results: the kernel writes the output itself
   return dli_paged_attention_mma(out, q, q_stride, k_pool, v_pool, block_tables, max_blocks, q_start, kv_len, seq0, num_seqs, 1,
-                                 first_row, nh, nkv, page_size, window, scale, -INFINITY, splits, part_acc, part_ml, stream);
+                                 first_row, nh, nkv, page_size, window, scale, -INFINITY, nullptr, splits, part_acc, part_ml, stream);
 }

@@ -264,7 +264,7 @@ template <typename T>
 __global__ void latent_prep_kernel(T* __restrict__ q_out, const T* __restrict__ proj, long long proj_stride,
                                    const float* __restrict__ w_norm, float eps, const int* __restrict__ positions,
                                    const float* __restrict__ inv_freq, const int* __restrict__ slots, T* __restrict__ k_pool, int nh,
-                                   int d, int dr, int r, int rot, int page_size) {
+                                   int d, int dr, int r, int rot, int page_size, float amp) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float trig[];  // cos[half] | sin[half]
@@ -274,7 +274,12 @@ __global__ void latent_prep_kernel(T* __restrict__ q_out, const T* __restrict__ 
   const T* src = proj + (size_t)t * proj_stride;
   const T* down = src + (size_t)nh * (d + dr);
   const float pos = (float)positions[t];
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf(pos * inv_freq[i], &sn, &cs);
+    trig[i] = cs * amp;  // amp: one factor on every cosine and sine (1: none)
+    trig[half + i] = sn * amp;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < r; i += blockDim.x) {
     const float x = to_float(down[i]);
@@ -306,7 +311,7 @@ __global__ void latent_prep_kernel(T* __restrict__ q_out, const T* __restrict__ 
 
 DLI_EXPORT int dli_latent_prep(void* q_out, const void* proj, long long proj_stride, const float* w_norm, float eps, const int* positions,
                                const float* inv_freq, const int* slots, void* k_pool, int n, int nh, int d, int dr, int r, int rot,
-                               int page_size, int dtype, cudaStream_t stream) {
+                               int page_size, float amp, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (nh < 1 || d < 1 || dr < 0 || r < 1 || rot < 0 || rot > dr || (rot & 1) || (rot && !inv_freq) || (slots && !k_pool) || page_size < 1 ||
       rot * sizeof(float) > 48 * 1024)
@@ -317,11 +322,96 @@ DLI_EXPORT int dli_latent_prep(void* q_out, const void* proj, long long proj_str
   cudaError_t e;
   if (dtype == DLI_F32)
     e = launch_pdl((latent_prep_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)q_out, (const float*)proj, proj_stride,
-                   w_norm, eps, positions, inv_freq, slots, (float*)k_pool, nh, d, dr, r, rot, page_size);
+                   w_norm, eps, positions, inv_freq, slots, (float*)k_pool, nh, d, dr, r, rot, page_size, amp);
   else
     e = launch_pdl((latent_prep_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)q_out,
                    (const __nv_bfloat16*)proj, proj_stride, w_norm, eps, positions, inv_freq, slots, (__nv_bfloat16*)k_pool, nh, d, dr, r,
-                   rot, page_size);
+                   rot, page_size, amp);
+  return (int)e;
+}
+
+// ---------------------------------------------------------------- rotation, then a unit root mean square per head, then the pages
+// One block per token, a warp per head.  x row: q (nh heads of d) | k (nkv heads of d) | v (nkv heads of dv), as the
+// convolution left them.  Every q and k head is rotated on its first `rot` dimensions (rotate-half pairing, angle
+// float32(position) * inv_freq[i]) and then, if unit_eps >= 0, divided by sqrt(mean(head^2) + unit_eps), all in float32.
+// Rows of D = max(d, dv) numbers leave, the shorter of keys and values padded with zeros:
+//   q -> q_out [n][nh][D];   k -> k_pool, v -> v_pool [pages][nkv][page_size][D] at the token's slot (if slots)
+template <typename T>
+__global__ void rotary_unit_store_kernel(T* __restrict__ q_out, const T* __restrict__ x, long long x_stride, const int* __restrict__ positions,
+                                         const float* __restrict__ inv_freq, const int* __restrict__ slots, T* __restrict__ k_pool,
+                                         T* __restrict__ v_pool, int nh, int nkv, int d, int dv, int D, int rot, float unit_eps, int page_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];  // cos[half] | sin[half] | a head of d floats per warp
+  const int t = blockIdx.x;
+  const int half = rot >> 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  float* trig = sm;
+  float* buf = sm + rot + (size_t)warp * d;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * inv_freq[i], &trig[half + i], &trig[i]);
+  __syncthreads();
+  const T* src = x + (size_t)t * x_stride;
+  const int slot = slots ? slots[t] : -1;
+  const long long page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? slot % page_size : 0;
+  for (int head = warp; head < nh + 2 * nkv; head += warps) {
+    if (head >= nh + nkv) {  // a value head: copied, padded
+      if (slot < 0) continue;
+      const int g = head - nh - nkv;
+      const T* part = src + (size_t)(nh + nkv) * d + (size_t)g * dv;
+      T* dst = v_pool + ((page * nkv + g) * page_size + off) * D;
+      for (int i = lane; i < D; i += 32) dst[i] = i < dv ? part[i] : from_float<T>(0.f);
+      continue;
+    }
+    const T* part = src + (size_t)head * d;
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      float v;
+      if (i < half) {
+        v = to_float(part[i]) * trig[i] - to_float(part[i + half]) * trig[half + i];
+      } else if (i < rot) {
+        v = to_float(part[i]) * trig[i - half] + to_float(part[i - half]) * trig[i];
+      } else {
+        v = to_float(part[i]);
+      }
+      buf[i] = v;
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = unit_eps >= 0.f ? 1.f / sqrtf(ss / (float)d + unit_eps) : 1.f;
+    T* dst;
+    if (head < nh) {
+      dst = q_out + ((size_t)t * nh + head) * D;
+    } else {
+      if (slot < 0) { __syncwarp(); continue; }
+      dst = k_pool + ((page * nkv + (head - nh)) * page_size + off) * D;
+    }
+    __syncwarp();
+    for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(i < d ? buf[i] * inv : 0.f);
+    __syncwarp();
+  }
+}
+
+DLI_EXPORT int dli_rotary_unit_store(void* q_out, const void* x, long long x_stride, const int* positions, const float* inv_freq,
+                                     const int* slots, void* k_pool, void* v_pool, int n, int nh, int nkv, int d, int dv, int rot,
+                                     float unit_eps, int page_size, int dtype, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (nh < 1 || nkv < 1 || d < 1 || dv < 1 || rot < 0 || rot > d || (rot & 1) || (rot && !inv_freq) || (slots && (!k_pool || !v_pool)) || page_size < 1)
+    return DLI_ERR_UNSUPPORTED;
+  const int D = d > dv ? d : dv;
+  const int heads = nh + 2 * nkv;
+  const int threads = heads >= 8 ? 256 : (heads >= 4 ? 128 : 64);
+  const size_t smem = ((size_t)rot + (size_t)(threads / 32) * d) * sizeof(float);
+  if (smem > 48 * 1024) return DLI_ERR_UNSUPPORTED;
+  cudaError_t e;
+  if (dtype == DLI_F32)
+    e = launch_pdl((rotary_unit_store_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, (float*)q_out, (const float*)x, x_stride, positions,
+                   inv_freq, slots, (float*)k_pool, (float*)v_pool, nh, nkv, d, dv, D, rot, unit_eps, page_size);
+  else
+    e = launch_pdl((rotary_unit_store_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, (__nv_bfloat16*)q_out,
+                   (const __nv_bfloat16*)x, x_stride, positions, inv_freq, slots, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh, nkv, d, dv, D,
+                   rot, unit_eps, page_size);
   return (int)e;
 }
 

@@ -13,7 +13,8 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
                                             const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                                             const int* __restrict__ block_tables, int max_blocks,
                                             const int* __restrict__ seq_of_token, const int* __restrict__ positions, int n,
-                                            int nh, int nkv, int d, int page_size, int window, float scale, float sink) {
+                                            int nh, int nkv, int d, int page_size, int window, float scale, float sink,
+                                            const float* __restrict__ sink_heads) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -67,7 +68,8 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
     }
     m = m_new;
   }
-  // a sink: one more term exp(sink) in the denominator that has no value (sink = -inf: none)
+  // a sink: one more term exp(sink) in the denominator that has no value (sink = -inf: none); a score per head if given
+  if (sink_heads) sink = sink_heads[h];
   if (sink != -CUDART_INF_F) l += expf(sink - m);
   const float inv = 1.f / l;
   T* o = out + (size_t)t * nh * d + (size_t)h * d;
@@ -81,7 +83,7 @@ __global__ void paged_attention_simt_kernel(T* __restrict__ out, const T* __rest
 DLI_EXPORT int dli_paged_attention_simt(void* out, const void* q, int q_stride, const void* k_pool, const void* v_pool,
                                         const int* block_tables, int max_blocks, const int* seq_of_token,
                                         const int* positions, int n, int nh, int nkv, int d, int page_size, int window,
-                                        float scale, float sink, int dtype, cudaStream_t stream) {
+                                        float scale, float sink, const float* sink_heads, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (d < 1 || d > 1024 || nkv < 1 || nh % nkv) return DLI_ERR_UNSUPPORTED;
   const int warps = 4;
@@ -91,7 +93,7 @@ DLI_EXPORT int dli_paged_attention_simt(void* out, const void* q, int q_stride, 
 #define DLI_SIMT(T, R)                                                                                                                  \
   launch_pdl((paged_attention_simt_kernel<T, R>), dim3(blocks), dim3(warps * 32), smem, stream, 1, (T*)out, (const T*)q, q_stride,       \
              (const T*)k_pool, (const T*)v_pool, block_tables, max_blocks, seq_of_token, positions, n, nh, nkv, d, page_size, window, \
-             scale, sink)
+             scale, sink, sink_heads)
   if (dtype == DLI_F32) {
     if (d <= 256) DLI_SIMT(float, 8);
     else DLI_SIMT(float, 32);

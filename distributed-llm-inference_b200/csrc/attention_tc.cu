@@ -50,6 +50,7 @@ struct Params {
   int seq0, nh, nkv, page_size, window;
   float scale_log2;
   float sink_log2;  // score of a sink (a term of the denominator without a value) times log2(e); -inf: none
+  const float* sink_heads;  // if not null: a sink score per query head (natural units), instead of sink_log2
   int tokens_per_tile, heads_per_chunk, head_chunks;
   int* error_flag;
 };
@@ -111,6 +112,10 @@ __device__ __forceinline__ float ex2(float x) {
 // What a sink adds to a denominator kept in units of 2^m (m in log2 units).
 __device__ __forceinline__ float sink_term(float sink_log2, float m) {
   return (sink_log2 == -CUDART_INF_F || m == -CUDART_INF_F) ? 0.f : exp2f(sink_log2 - m);
+}
+// The sink score of a query head, in log2 units.
+__device__ __forceinline__ float sink_of(const float* sink_heads, float sink_log2, int head) {
+  return sink_heads ? sink_heads[head] * 1.4426950408889634f : sink_log2;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -420,7 +425,7 @@ __global__ void __launch_bounds__(THREADS, 1) paged_prefill_tc_kernel(const __gr
     if (group == 0) asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");
     else asm volatile("bar.sync 2, %0;" ::"n"(SOFTMAX_THREADS / 2) : "memory");
     if (!*failed && rvalid) {
-      const float inv = 1.f / (rl[r] + rl[ROWS + r] + sink_term(p.sink_log2, m_ref * p.scale_log2));
+      const float inv = 1.f / (rl[r] + rl[ROWS + r] + sink_term(sink_of(p.sink_heads, p.sink_log2, head0 + (r - rtok * Gc)), m_ref * p.scale_log2));
       const size_t row = (size_t)(q0 + tok0 + rtok) * p.nh + head0 + (r - rtok * Gc);
       uint4* dst = reinterpret_cast<uint4*>(p.out + row * D + half * 32);
 #pragma unroll
@@ -784,7 +789,7 @@ __global__ void __launch_bounds__(T2Cfg<HD>::THREADS, 1) paged_prefill_tc2_kerne
     ok = wait_or_fail(my_o_done, (num_tiles - 1) & 1, failed, 13, p.error_flag) && ok;
     ok = __all_sync(0xffffffffu, ok);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const float inv = 1.f / (l + sink_term(p.sink_log2, m_ref * p.scale_log2));
+    const float inv = 1.f / (l + sink_term(sink_of(p.sink_heads, p.sink_log2, head0 + (r % Gc)), m_ref * p.scale_log2));
     const size_t row = (size_t)(q0 + tok0 + rtok) * p.nh + head0 + (r % Gc);
 #pragma unroll
     for (int c = 0; c < D; c += 32) {
@@ -847,7 +852,7 @@ int* error_flag_host = nullptr;
 DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
                                     const int* kv_len, int seq0, int num_seqs, int max_q_len, int nh, int nkv, int head_dim,
-                                    int page_size, int window, float scale, float sink, int query_tiles, cudaStream_t stream) {
+                                    int page_size, int window, float scale, float sink, const float* sink_heads, int query_tiles, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (head_dim != 64 && head_dim != 128) return DLI_ERR_UNSUPPORTED;
   if (nkv < 1 || nh % nkv || page_size < 8 || page_size > 128 || (KEYS % page_size) != 0) return DLI_ERR_UNSUPPORTED;
@@ -872,6 +877,7 @@ DLI_EXPORT int dli_paged_prefill_tc(void* out, const void* q, long long q_stride
   p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sink_log2 = sink * 1.4426950408889634f;  // -inf (no sink) stays -inf
+  p.sink_heads = sink_heads;
   const int G = nh / nkv;
   p.heads_per_chunk = G < ROWS ? G : ROWS;
   p.head_chunks = (G + p.heads_per_chunk - 1) / p.heads_per_chunk;
@@ -957,6 +963,7 @@ struct DecodeParams {
   int cluster_merge;  // the splits of a (sequence, head group) are one cluster and merge through shared memory
   float scale_log2;
   float sink_log2;  // as in Params
+  const float* sink_heads;  // as in Params
   float* part_acc;
   float* part_ml;
   int* error_flag;
@@ -1249,7 +1256,7 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
     }
     const size_t row = (size_t)token * p.nh + head0 + r;
     if (p.splits == 1) {
-      p.out[row * D + dcol] = __float2bfloat16_rn(acc / (L + sink_term(p.sink_log2, mx)));
+      p.out[row * D + dcol] = __float2bfloat16_rn(acc / (L + sink_term(sink_of(p.sink_heads, p.sink_log2, head0 + r), mx)));
     } else if (p.cluster_merge) {
       const uint32_t dst = smem_u32(recv + (split * owned_max + r / p.splits) * RECV_ROW);
       const int owner = r % p.splits;
@@ -1286,13 +1293,13 @@ __global__ void __launch_bounds__(DWARPS * 32) paged_decode_tma_kernel(const __g
         acc += part[dcol] * f;
       }
     }
-    p.out[((size_t)token * p.nh + head0 + r) * D + dcol] = __float2bfloat16_rn(acc / (L + sink_term(p.sink_log2, mx)));
+    p.out[((size_t)token * p.nh + head0 + r) * D + dcol] = __float2bfloat16_rn(acc / (L + sink_term(sink_of(p.sink_heads, p.sink_log2, head0 + r), mx)));
   }
 }
 
 // out[row] = sum_i acc_i 2^(m_i - max m) / sum_i l_i 2^(m_i - max m); one block per (token, head) row.
 __global__ void merge_decode_splits_kernel(bf16* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                           int row0, int splits, int d, float sink_log2) {
+                                           int row0, int splits, int d, float sink_log2, const float* __restrict__ sink_heads, int nh) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = (size_t)row0 + blockIdx.x;
@@ -1304,7 +1311,7 @@ __global__ void merge_decode_splits_kernel(bf16* __restrict__ out, const float* 
     const float mi = ml[2 * i];
     if (mi != -CUDART_INF_F) L += ml[2 * i + 1] * exp2f(mi - mmax);
   }
-  L += sink_term(sink_log2, mmax);
+  L += sink_term(sink_of(sink_heads, sink_log2, (int)(row % nh)), mmax);
   const float inv = 1.f / L;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float acc = 0.f;
@@ -1350,7 +1357,7 @@ int launch_decode_warps(const CUtensorMap& map_k, const CUtensorMap& map_v, cons
   if (e != cudaSuccess) return (int)e;
   if (p.splits > 1 && !p.cluster_merge)
     e = launch_pdl(merge_decode_splits_kernel, dim3(num_seqs * p.nh), dim3(64), 0, stream, 1, p.out, (const float*)p.part_acc,
-                   (const float*)p.part_ml, first_row * p.nh, p.splits, HD, p.sink_log2);
+                   (const float*)p.part_ml, first_row * p.nh, p.splits, HD, p.sink_log2, p.sink_heads, p.nh);
   return (int)e;
 }
 
@@ -1375,7 +1382,7 @@ int launch_decode(const CUtensorMap& map_k, const CUtensorMap& map_v, const Deco
 DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride, const void* k_pool, const void* v_pool,
                                     long long num_pages, const int* block_tables, int max_blocks, const int* q_start,
                                     const int* kv_len, int seq0, int num_seqs, int first_row, int nh, int nkv, int head_dim,
-                                    int page_size, int window, float scale, float sink, int splits, float* part_acc, float* part_ml,
+                                    int page_size, int window, float scale, float sink, const float* sink_heads, int splits, float* part_acc, float* part_ml,
                                     int max_kv_len, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (head_dim != 64 && head_dim != 128) return DLI_ERR_UNSUPPORTED;
@@ -1398,6 +1405,7 @@ DLI_EXPORT int dli_paged_decode_tma(void* out, const void* q, long long q_stride
   p.nh = nh; p.nkv = nkv; p.page_size = page_size; p.window = window; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sink_log2 = sink * 1.4426950408889634f;  // -inf (no sink) stays -inf
+  p.sink_heads = sink_heads;
   p.part_acc = part_acc; p.part_ml = part_ml; p.error_flag = error_flag_device;
   p.cluster_merge = merges_in_cluster(nh, nkv, splits);
   return head_dim == 64 ? launch_decode<64>(map_k, map_v, p, num_seqs, first_row, max_kv_len, stream)

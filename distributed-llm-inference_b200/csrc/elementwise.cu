@@ -623,10 +623,11 @@ DLI_EXPORT int dli_silu_mul(void* out, const void* gu, int n, int I, int tiled, 
 }
 
 // ---------------------------------------------------------------- activation of a plain (ungated) feed-forward
-// x <- act(x) in place; kinds: 0 relu(x)^2, 1 gelu with the tanh approximation, 2 silu.
+// x <- act(x) in place; kinds: 0 relu(x)^2, 1 gelu with the tanh approximation, 2 silu, 3 tanh.
 #define DLI_ACT_RELU2 0
 #define DLI_ACT_GELU_TANH 1
 #define DLI_ACT_SILU 2
+#define DLI_ACT_TANH 3
 
 __device__ __forceinline__ float apply_activation(float z, int kind) {
   if (kind == DLI_ACT_RELU2) {
@@ -634,6 +635,7 @@ __device__ __forceinline__ float apply_activation(float z, int kind) {
     return r * r;
   }
   if (kind == DLI_ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == DLI_ACT_TANH) return tanhf(z);
   return z / (1.f + expf(-z));
 }
 
@@ -660,7 +662,7 @@ __global__ void activation_bf16_vec_kernel(__nv_bfloat16* __restrict__ x, size_t
 
 DLI_EXPORT int dli_activation(void* x, long long total, int kind, int dtype, cudaStream_t stream) {
   if (total == 0) return 0;
-  if (kind < 0 || kind > 2) return DLI_ERR_UNSUPPORTED;
+  if (kind < 0 || kind > 3) return DLI_ERR_UNSUPPORTED;
   const int threads = 256;
   const size_t cap = (size_t)sm_count() * 16;
   if (dtype == DLI_BF16 && total % 8 == 0 && ((uintptr_t)x % 16) == 0) {

@@ -12,6 +12,10 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 // for outputs that are rounded to bfloat16 anyway: the fast exponential and division (a few ulp of float32)
 template <typename T> __device__ __forceinline__ float silu_out(float x) { return silu(x); }
 template <> __device__ __forceinline__ float silu_out<__nv_bfloat16>(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+// what follows the convolution: SiLU (act != 0) or nothing
+template <typename T> __device__ __forceinline__ float conv_out(int act, float x) { return act ? silu_out<T>(x) : x; }
+// the gate of the group norm: SiLU, or (mode 2) the logistic function
+__device__ __forceinline__ float norm_gate(float z, int mode) { return mode == 2 ? 1.f / (1.f + expf(-z)) : silu(z); }
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // out[t, c] = silu(bias[c] + sum_j w[j, c] * in(t - (taps - 1) + j, c)) (w [taps, C]: a tap's weights are contiguous);
@@ -22,7 +26,7 @@ template <typename T>
 __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict__ u, long long u_stride, int col0,
                                         const float* __restrict__ w, const float* __restrict__ bias, const T* __restrict__ state,
                                         const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                                        const int* __restrict__ state_slot, int C, int taps) {
+                                        const int* __restrict__ state_slot, int C, int taps, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -38,7 +42,7 @@ __global__ void causal_conv_silu_kernel(T* __restrict__ out, const T* __restrict
     const float x = r >= 0 ? to_float(u[(size_t)(first + r) * u_stride + col0 + c]) : to_float(carried[(size_t)(taps - 1 + r) * C + c]);
     acc = fmaf(w[(size_t)j * C + c], x, acc);
   }
-  out[(size_t)t * C + c] = from_float<T>(silu_out<T>(acc));
+  out[(size_t)t * C + c] = from_float<T>(conv_out<T>(act, acc));
 }
 
 // The same, eight channels a thread with 16-byte accesses (C, col0 and the row strides multiples of 8).  A block takes
@@ -48,7 +52,7 @@ template <typename T>
 __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __restrict__ u, long long u_stride, int col0,
                                             const float* __restrict__ w, const float* __restrict__ bias, const T* __restrict__ state,
                                             const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                                            const int* __restrict__ state_slot, int n, int C, int taps) {
+                                            const int* __restrict__ state_slot, int n, int C, int taps, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -75,7 +79,7 @@ __global__ void causal_conv_silu_vec_kernel(T* __restrict__ out, const T* __rest
     for (int k = 0; k < 8; ++k) acc[k] = fmaf(wv[k], x[k], acc[k]);
   }
 #pragma unroll
-  for (int k = 0; k < 8; ++k) acc[k] = silu_out<T>(acc[k]);
+  for (int k = 0; k < 8; ++k) acc[k] = conv_out<T>(act, acc[k]);
   store8(out + (size_t)t * C + c, acc);
 }
 
@@ -87,7 +91,7 @@ template <typename T, int TAPS>
 __global__ void causal_conv_silu_window_kernel(T* __restrict__ out, const T* __restrict__ u, long long u_stride, int col0,
                                                const float* __restrict__ w, const float* __restrict__ bias, const T* __restrict__ state,
                                                const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                                               const int* __restrict__ state_slot, int n, int C) {
+                                               const int* __restrict__ state_slot, int n, int C, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
@@ -135,7 +139,7 @@ __global__ void causal_conv_silu_window_kernel(T* __restrict__ out, const T* __r
       float a = bv[k];
 #pragma unroll
       for (int j = 0; j < TAPS - 1; ++j) a = fmaf(wv[j][k], win[j][k], a);
-      acc[k] = silu_out<T>(fmaf(wv[TAPS - 1][k], cur[i][k], a));
+      acc[k] = conv_out<T>(act, fmaf(wv[TAPS - 1][k], cur[i][k], a));
     }
     store8(out + (size_t)t * C + c, acc);
 #pragma unroll
@@ -397,12 +401,12 @@ __global__ void gated_group_rmsnorm_kernel(T* __restrict__ out, const float* __r
   const T* zrow = u + (size_t)t * u_stride + z_col + c0;
   float q = 0.f;
   for (int i = threadIdx.x; i < size; i += blockDim.x) {
-    const float gv = gate_after ? yrow[i] : yrow[i] * silu(to_float(zrow[i]));
+    const float gv = gate_after ? yrow[i] : yrow[i] * norm_gate(to_float(zrow[i]), gate_after);
     q = fmaf(gv, gv, q);
   }
   const float r = 1.f / sqrtf(block_sum(q, red) / (float)size + eps);
   for (int i = threadIdx.x; i < size; i += blockDim.x) {
-    const float gate = silu(to_float(zrow[i]));
+    const float gate = norm_gate(to_float(zrow[i]), gate_after);
     out[(size_t)t * inner + c0 + i] = from_float<T>(gate_after ? yrow[i] * r * w[c0 + i] * gate : yrow[i] * gate * r * w[c0 + i]);
   }
 }
@@ -432,7 +436,7 @@ __global__ void __launch_bounds__(THREADS) gated_group_rmsnorm_vec_kernel(T* __r
       load8(zrow + col, z);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const float gate = silu(z[k]);
+        const float gate = norm_gate(z[k], gate_after);
         q = gate_after ? fmaf(gv[c][k], gv[c][k], q) : fmaf(gv[c][k] * gate, gv[c][k] * gate, q);
         gv[c][k] *= gate;  // the gate is a factor of the output either way
       }
@@ -520,7 +524,7 @@ int launch_scan(float* y, const T* xbc, const T* u, long long u_stride, int dt_c
 
 DLI_EXPORT int dli_causal_conv_silu(void* out, const void* u, long long u_stride, int col0, const float* w, const float* bias,
                                     const void* state, const int* seq_of_token, const int* q_start, const int* state_slot, int n, int C,
-                                    int taps, int dtype, cudaStream_t stream) {
+                                    int taps, int act, int dtype, cudaStream_t stream) {
   if (n == 0) return 0;
   if (C < 1 || taps < 1 || (C + 127) / 128 > 65535) return DLI_ERR_UNSUPPORTED;
   cudaError_t e;
@@ -531,7 +535,7 @@ DLI_EXPORT int dli_causal_conv_silu(void* out, const void* u, long long u_stride
       const dim3 wgrid((n + CONV_TOKS - 1) / CONV_TOKS, (items + wt - 1) / wt);
 #define DLI_CONV_WIN(T, TAPS)                                                                                                      \
   return (int)launch_pdl((causal_conv_silu_window_kernel<T, TAPS>), wgrid, dim3(wt), 0, stream, 1, (T*)out, (const T*)u, u_stride, col0, w, \
-                         bias, (const T*)state, seq_of_token, q_start, state_slot, n, C)
+                         bias, (const T*)state, seq_of_token, q_start, state_slot, n, C, act)
       if (dtype == DLI_F32) {
         if (taps == 2) DLI_CONV_WIN(float, 2);
         if (taps == 3) DLI_CONV_WIN(float, 3);
@@ -546,19 +550,19 @@ DLI_EXPORT int dli_causal_conv_silu(void* out, const void* u, long long u_stride
     const dim3 vblock(32, 8), vgrid((n + 7) / 8, (items + 31) / 32);
     if (dtype == DLI_F32)
       e = launch_pdl((causal_conv_silu_vec_kernel<float>), vgrid, vblock, 0, stream, 1, (float*)out, (const float*)u, u_stride, col0, w, bias,
-                     (const float*)state, seq_of_token, q_start, state_slot, n, C, taps);
+                     (const float*)state, seq_of_token, q_start, state_slot, n, C, taps, act);
     else
       e = launch_pdl((causal_conv_silu_vec_kernel<__nv_bfloat16>), vgrid, vblock, 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)u,
-                     u_stride, col0, w, bias, (const __nv_bfloat16*)state, seq_of_token, q_start, state_slot, n, C, taps);
+                     u_stride, col0, w, bias, (const __nv_bfloat16*)state, seq_of_token, q_start, state_slot, n, C, taps, act);
     return (int)e;
   }
   const dim3 grid(n, (C + 127) / 128), block(128);
   if (dtype == DLI_F32)
     e = launch_pdl((causal_conv_silu_kernel<float>), grid, block, 0, stream, 1, (float*)out, (const float*)u, u_stride, col0, w, bias,
-                   (const float*)state, seq_of_token, q_start, state_slot, C, taps);
+                   (const float*)state, seq_of_token, q_start, state_slot, C, taps, act);
   else
     e = launch_pdl((causal_conv_silu_kernel<__nv_bfloat16>), grid, block, 0, stream, 1, (__nv_bfloat16*)out, (const __nv_bfloat16*)u, u_stride,
-                   col0, w, bias, (const __nv_bfloat16*)state, seq_of_token, q_start, state_slot, C, taps);
+                   col0, w, bias, (const __nv_bfloat16*)state, seq_of_token, q_start, state_slot, C, taps, act);
   return (int)e;
 }
 

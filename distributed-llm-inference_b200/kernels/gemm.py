@@ -88,6 +88,21 @@ def project(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_t
     return y if out_dtype in (None, y.dtype) else y.to(out_dtype)
 
 
+def project_bias(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    """y = x W^T + b: the bias joins the float32 sums before the one rounding (the library's product with its bias
+    epilogue, at every token count); without a bias it is ``project``."""
+    if bias is None:
+        return project(x, weight)
+    return linear_bias(x, weight, bias)
+
+
+def linear_bias(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    _need_device(x, "linear_bias")
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("linear_bias: TF32 was switched on; the float32 path must stay true 32-bit")
+    return torch.addmm(bias, x, weight.t())
+
+
 def last_product(x: torch.Tensor, weight: torch.Tensor, defer: bool):
     """The product that ends a mixer or feed-forward: x W^T, or — if the part's owner allowed it and
     the decode kernel with its fused epilogues will serve these tokens — the product left
@@ -134,6 +149,15 @@ def heads_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate
     if gate is not None:
         ops.sigmoid_gate(out.view(n, heads * features), gate)
     return out
+
+
+def batched_project(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """out[b] = x[b] @ weight[b] for x [batch, n, in] and weight [batch, in, features] (several products of one shape whose
+    inputs differ, in one call of the library's batched product); float32 accumulation."""
+    _need_device(x, "batched_project")
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise RuntimeError("batched_project: TF32 was switched on; the float32 path must stay true 32-bit")
+    return torch.bmm(x, weight)
 
 
 def logits_product(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -55,10 +55,21 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
-def _sink(sink: float | None) -> float:
+def _sink(sink) -> float:
     """The attention kernels' sink argument: the score of one more term of the softmax denominator that has no
-    value (exp(sink) is added to the sum of the exponentials), or -inf for none."""
-    return float("-inf") if sink is None else float(sink)
+    value (exp(sink) is added to the sum of the exponentials), or -inf for none (also when a tensor gives a score per
+    query head: ``_sink_heads``)."""
+    return float("-inf") if sink is None or isinstance(sink, torch.Tensor) else float(sink)
+
+
+def _sink_heads(sink, num_heads: int) -> c_void_p:
+    """The attention kernels' second sink argument: a float32 score per query head (a learned sink), or null."""
+    if not isinstance(sink, torch.Tensor):
+        return c_void_p(0)
+    _need(sink, "sink", torch.float32)
+    if sink.numel() != num_heads:
+        raise KernelError("a sink per head needs one score for every query head")
+    return _ptr(sink)
 
 
 def _need(t: torch.Tensor, name: str, dtype: torch.dtype | None = None) -> None:
@@ -309,11 +320,11 @@ def paged_attention_simt(
         raise KernelError(f"paged_attention_simt: head_dim {d} (<= {SIMT_MAX_HEAD_DIM}) / heads {num_heads} per kv head {nkv} not supported")
     f = _fn(
         "attention_simt.cu", "dli_paged_attention_simt",
-        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_float, c_int, c_void_p],
+        [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_float, c_void_p, c_int, c_void_p],
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1],
-          _ptr(seq_of_token), _ptr(positions), n, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), DT_CODE[out.dtype], _stream()),
+          _ptr(seq_of_token), _ptr(positions), n, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), _sink_heads(sink, num_heads), DT_CODE[out.dtype], _stream()),
         "paged_attention_simt",
     )
 
@@ -355,13 +366,13 @@ def paged_prefill_tc(
         raise KernelError("paged_prefill_tc: sequence range outside the batch")
     f = _fn(
         "attention_tc.cu", "dli_paged_prefill_tc",
-        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_float, c_int, c_void_p],
+        [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_float, c_void_p, c_int, c_void_p],
     )
     if query_tiles not in (0, 1, 2):
         raise KernelError("paged_prefill_tc: query_tiles is 0 (choose), 1 or 2")
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), query_tiles, _stream()),
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), _sink_heads(sink, num_heads), query_tiles, _stream()),
         "paged_prefill_tc",
     )
 
@@ -415,12 +426,12 @@ def paged_decode_tma(
     f = _fn(
         "attention_tc.cu", "dli_paged_decode_tma",
         [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 8
-        + [c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p],
+        + [c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_tables), block_tables.shape[1],
-          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), splits,
-          _ptr(acc), _ptr(ml), int(max_kv_len), _stream()),
+          _ptr(q_start), _ptr(kv_len), seq0, num_seqs, first_row, num_heads, nkv, d, page_size, int(window or 0), scale, _sink(sink), _sink_heads(sink, num_heads),
+          splits, _ptr(acc), _ptr(ml), int(max_kv_len), _stream()),
         "paged_decode_tma",
     )
     global launch_count
@@ -561,13 +572,13 @@ def paged_attention_mma(
     f = _fn(
         "attention_mma.cu", "dli_paged_attention_mma",
         [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
-        + [c_int] * 8 + [c_float, c_float, c_int, c_void_p, c_void_p, c_void_p],
+        + [c_int] * 8 + [c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
         {"HEAD_DIM": d},
     )
     _check(
         f(_ptr(out), _ptr(qkv), qkv.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), block_tables.shape[1],
           _ptr(q_start), _ptr(kv_len), seq0, num_seqs, max_q_len, first_row, num_heads, nkv, page_size, int(window or 0),
-          scale, _sink(sink), splits, _ptr(acc), _ptr(ml), _stream()),
+          scale, _sink(sink), _sink_heads(sink, num_heads), splits, _ptr(acc), _ptr(ml), _stream()),
         "paged_attention_mma",
     )
     global launch_count
@@ -930,16 +941,17 @@ def stream_reinject(h: torch.Tensor, table: torch.Tensor | None, ids: torch.Tens
 
 
 def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
-    """x <- act(x) in place and returned: ``relu2`` (the square of relu), ``gelu_tanh``, ``silu``."""
+    """x <- act(x) in place and returned: ``relu2`` (the square of relu), ``gelu_tanh``, ``silu``, ``tanh``."""
     _need(x, "x")
-    if x.dtype not in DT_CODE or kind not in ACTIVATIONS:
-        raise KernelError(f"activation: dtype {x.dtype} or kind {kind!r} (known: {sorted(ACTIVATIONS)}) not supported")
+    if x.dtype not in DT_CODE or kind not in ELEMENTWISE_ACTIVATIONS:
+        raise KernelError(f"activation: dtype {x.dtype} or kind {kind!r} (known: {sorted(ELEMENTWISE_ACTIVATIONS)}) not supported")
     f = _fn("elementwise.cu", "dli_activation", [c_void_p, c_longlong, c_int, c_int, c_void_p])
-    _check(f(_ptr(x), x.numel(), ACTIVATIONS[kind], DT_CODE[x.dtype], _stream()), "activation")
+    _check(f(_ptr(x), x.numel(), ELEMENTWISE_ACTIVATIONS[kind], DT_CODE[x.dtype], _stream()), "activation")
     return x
 
 
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}  # what a plain feed-forward may use (also in the products' epilogues)
+ELEMENTWISE_ACTIVATIONS = {**ACTIVATIONS, "tanh": 3}  # what the kernel of its own takes
 
 
 # ------------------------------------------------------------------ between an attention mixer's projections and its kernel
@@ -996,12 +1008,12 @@ def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> None:
 
 def latent_prep(q_out: torch.Tensor, proj: torch.Tensor, w_norm: torch.Tensor, eps: float, positions: torch.Tensor,
                 inv_freq: torch.Tensor | None, slots: torch.Tensor | None, k_pool: torch.Tensor | None, num_heads: int, head_dim: int,
-                rot_dim: int, kv_rank: int, rotary_dim: int, page_size: int) -> None:
+                rot_dim: int, kv_rank: int, rotary_dim: int, page_size: int, amp: float = 1.0) -> None:
     """Between the projections of an attention over a cached latent and its attention kernel, one kernel a step.
     proj [n, >= nh (d + dr) + r + dr]: per head d plain and dr rotated query numbers, then the down projection: r latent
     numbers and dr of a key part that all heads share.  The latent is divided by its RMS (``eps`` inside the root) and
     multiplied by ``w_norm`` [r]; the first ``rotary_dim`` of the dr numbers of the key part and of every head's query part
-    are rotated (rotate-half pairing, angle float32(position) * inv_freq[i]).  The cache row latent | key part goes to
+    are rotated (rotate-half pairing, angle float32(position) * inv_freq[i], cosines and sines times ``amp``).  The cache row latent | key part goes to
     ``k_pool`` [pages, 1, page_size, r + dr] at ``slots`` (if given); the rotated query parts go to columns r .. r + dr of
     every head of ``q_out`` [n, nh (r + dr)], whose other columns this kernel leaves alone."""
     _need(positions, "positions", torch.int32), _need(q_out, "q_out"), _need(w_norm, "w_norm", torch.float32)
@@ -1022,10 +1034,40 @@ def latent_prep(q_out: torch.Tensor, proj: torch.Tensor, w_norm: torch.Tensor, e
         if tuple(k_pool.shape[1:]) != (1, page_size, row) or slots.numel() != n:
             raise KernelError("latent_prep: pool layout must be [pages, 1, page_size, kv_rank + rot_dim]")
     f = _fn("attention_prep.cu", "dli_latent_prep",
-            [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_void_p])
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_int, c_void_p])
     _check(f(_ptr(q_out), _ptr(proj), proj.stride(0), _ptr(w_norm), eps, _ptr(positions), _ptr(inv_freq if rotary_dim else None),
              _ptr(slots if write else None), _ptr(k_pool if write else None), n, num_heads, head_dim, rot_dim, kv_rank, rotary_dim, page_size,
-             DT_CODE[proj.dtype], _stream()), "latent_prep")
+             float(amp), DT_CODE[proj.dtype], _stream()), "latent_prep")
+
+
+def rotary_unit_store(q_out: torch.Tensor, x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, slots: torch.Tensor | None,
+                      k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                      rotary_dim: int, unit_eps: float | None, page_size: int) -> None:
+    """Between an attention mixer's convolutions and its attention kernel, one kernel a step.  x [n, (nh + nkv) d + nkv dv]: q | k | v.
+    Every q and k head is rotated on its first ``rotary_dim`` dimensions (rotate-half pairing, angle float32(position) *
+    inv_freq[i]) and then, unless ``unit_eps`` is None, divided by sqrt(mean(head^2) + unit_eps); float32 throughout, one rounding.
+    Rows of D = max(d, dv) numbers leave, the shorter of keys and values padded with zeros: q to ``q_out`` [n, nh D], k and v to
+    the pools [pages, nkv, page_size, D] at ``slots`` (if given)."""
+    _need(positions, "positions", torch.int32), _need(q_out, "q_out"), _need(x, "x", q_out.dtype)
+    n = x.shape[0]
+    D = max(head_dim, value_dim)
+    if (x.dtype not in DT_CODE or x.shape[1] != (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim or positions.numel() != n
+            or tuple(q_out.shape) != (n, num_heads * D) or rotary_dim % 2 or rotary_dim > head_dim):
+        raise KernelError("rotary_unit_store: shapes do not agree")
+    if rotary_dim:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("rotary_unit_store: inv_freq must have rotary_dim / 2 entries")
+    write = slots is not None
+    if write:
+        _need(slots, "slots", torch.int32), _need(k_pool, "k_pool", x.dtype), _need(v_pool, "v_pool", x.dtype)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, D) or k_pool.shape != v_pool.shape or slots.numel() != n:
+            raise KernelError("rotary_unit_store: pool layout must be [pages, kv_heads, page_size, max(head_dim, value_dim)]")
+    f = _fn("attention_prep.cu", "dli_rotary_unit_store",
+            [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_int, c_int, c_void_p])
+    _check(f(_ptr(q_out), _ptr(x), x.stride(0), _ptr(positions), _ptr(inv_freq if rotary_dim else None), _ptr(slots if write else None),
+             _ptr(k_pool if write else None), _ptr(v_pool if write else None), n, num_heads, num_kv_heads, head_dim, value_dim, rotary_dim,
+             -1.0 if unit_eps is None else float(unit_eps), page_size, DT_CODE[x.dtype], _stream()), "rotary_unit_store")
 
 
 def heads_matvec_supported(in_features: int, features: int) -> bool:
@@ -1067,9 +1109,9 @@ def _columns(u: torch.Tensor, name: str) -> None:
 
 
 def causal_conv_silu(out: torch.Tensor, u: torch.Tensor, col0: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
-                     seq_of_token: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor) -> None:
+                     seq_of_token: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, activation: bool = True) -> None:
     """out[t, c] = silu(bias[c] + sum_j weight[j, c] * in(t - (taps - 1) + j, c)) for channels c = columns col0 .. of u
-    (``weight`` [taps, C]: each tap's weights lie together).
+    (``weight`` [taps, C]: each tap's weights lie together); with ``activation`` false the sum itself, without SiLU.
     The last tap weighs the token itself; in() before the step's first token of a sequence is the sequence's carried
     input in ``state`` [slots, taps - 1, C] (oldest first).  ``conv_state_update`` moves the state on afterwards."""
     _columns(u, "causal_conv_silu"), _need(out, "out", u.dtype), _need(weight, "weight", torch.float32), _need(state, "state", u.dtype)
@@ -1081,9 +1123,9 @@ def causal_conv_silu(out: torch.Tensor, u: torch.Tensor, col0: int, weight: torc
     if bias is not None:
         _need(bias, "bias", torch.float32)
     f = _fn("ssm.cu", "dli_causal_conv_silu", [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                              c_int, c_int, c_int, c_int, c_void_p])
+                                              c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(out), _ptr(u), u.stride(0), col0, _ptr(weight), _ptr(bias), _ptr(state), _ptr(seq_of_token), _ptr(q_start), _ptr(state_slot),
-             n, C, taps, DT_CODE[u.dtype], _stream()), "causal_conv_silu")
+             n, C, taps, int(activation), DT_CODE[u.dtype], _stream()), "causal_conv_silu")
 
 
 def conv_state_update(state: torch.Tensor, u: torch.Tensor, col0: int, q_start: torch.Tensor, state_slot: torch.Tensor) -> None:
@@ -1123,16 +1165,20 @@ def ssm_scan(y: torch.Tensor, xbc: torch.Tensor, u: torch.Tensor, dt_col: int, d
 
 
 def gated_group_rmsnorm(out: torch.Tensor, y: torch.Tensor, u: torch.Tensor, z_col: int, weight: torch.Tensor, parts: int, eps: float,
-                        gate_after: bool = False) -> None:
+                        gate_after: bool = False, gate: str = "silu") -> None:
     """out = g / sqrt(mean(g^2) + eps) * weight with g = y * silu(z), the mean taken over each of ``parts`` equal runs
     of the row; z is columns z_col .. of u; y float32.  ``gate_after``: the gate stays out of the norm,
-    out = y / sqrt(mean(y^2) + eps) * weight * silu(z)."""
+    out = y / sqrt(mean(y^2) + eps) * weight * silu(z); with ``gate`` = ``"sigmoid"`` (only behind the norm) the gate is
+    the logistic function of z instead of SiLU."""
+    if gate not in ("silu", "sigmoid") or (gate == "sigmoid" and not gate_after):
+        raise KernelError("gated_group_rmsnorm: gate is silu, or sigmoid behind the norm")
     _columns(u, "gated_group_rmsnorm"), _need(out, "out", u.dtype), _need(y, "y", torch.float32), _need(weight, "weight", torch.float32)
     n, inner = y.shape
     if tuple(out.shape) != (n, inner) or u.shape[0] != n or z_col + inner > u.shape[1] or weight.numel() != inner or inner % parts:
         raise KernelError("gated_group_rmsnorm: shapes do not agree")
     f = _fn("ssm.cu", "dli_gated_group_rmsnorm", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p])
-    _check(f(_ptr(out), _ptr(y), _ptr(u), u.stride(0), z_col, _ptr(weight), n, inner, parts, eps, int(gate_after), DT_CODE[u.dtype], _stream()),
+    mode = 2 if gate == "sigmoid" else int(gate_after)
+    _check(f(_ptr(out), _ptr(y), _ptr(u), u.stride(0), z_col, _ptr(weight), n, inner, parts, eps, mode, DT_CODE[u.dtype], _stream()),
            "gated_group_rmsnorm")
 
 
@@ -1379,3 +1425,185 @@ def diff_attention_scratch(num_seqs: int, num_heads: int, vdim: int, splits: int
     """float32 numbers of the scratch in which ``splits`` CTAs leave a single token's partial results: for every sequence,
     head, split and map the unnormalised outputs, their maximum and their sum."""
     return num_seqs * num_heads * splits * 2 * (vdim + 2)
+
+
+# ------------------------------------------------------------------ a stream whose sublayer outputs carry a learned scale per feature
+
+
+def add_rmsnorm_scaled(y: torch.Tensor | None, h: torch.Tensor, a: torch.Tensor | None, fa: float, b: torch.Tensor | None, fb: float,
+                       scale: torch.Tensor | None, weight: torch.Tensor | None, eps: float, rows: torch.Tensor | None = None) -> None:
+    """v = h[s] + scale * (fa * a[s] + fb * b[s]) with s = rows[r] (or r); y[r] = v / sqrt(mean(v^2) + eps) * weight.
+    ``b`` may be None (one output), ``a`` too (nothing is added).  Without ``rows`` the sum is written back to ``h``; with
+    ``y`` None only the addition happens.  float32 arithmetic, one rounding."""
+    _need(h, "h", torch.float32)
+    H = h.shape[1]
+    n_rows = h.shape[0] if rows is None else rows.numel()
+    dtype = y.dtype if y is not None else (a.dtype if a is not None else torch.float32)
+    if dtype not in DT_CODE:
+        raise KernelError("add_rmsnorm_scaled: dtype not supported")
+    if y is not None:
+        _need(y, "y", dtype), _need(weight, "weight", torch.float32)
+        if tuple(y.shape) != (n_rows, H) or weight.numel() != H:
+            raise KernelError("add_rmsnorm_scaled: y or weight has the wrong shape")
+    for t, name in ((a, "a"), (b, "b")):
+        if t is not None:
+            _need(t, name, dtype)
+            if t.shape != h.shape:
+                raise KernelError(f"add_rmsnorm_scaled: {name} must have the stream's shape")
+    if a is not None:
+        _need(scale, "scale", torch.float32)
+        if scale.numel() != H:
+            raise KernelError("add_rmsnorm_scaled: one scale per feature")
+    if b is not None and a is None:
+        raise KernelError("add_rmsnorm_scaled: b without a")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if y is None and (rows is not None or a is None):
+        return
+    f = _fn("stream_ops.cu", "dli_add_rmsnorm_scaled", [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_float, c_void_p,
+                                                        c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(h), _ptr(a), float(fa), _ptr(b), float(fb), _ptr(scale), _ptr(weight), eps, _ptr(rows), n_rows, H, DT_CODE[dtype], _stream()),
+           "add_rmsnorm_scaled")
+
+
+def concat_stream_rows(out: torch.Tensor, h: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """out[t] = [h[t] rounded to out's dtype | table[ids[t]]]: the stream and the embedding of the step's tokens side by side."""
+    _need(out, "out"), _need(h, "h", torch.float32), _need(table, "table", out.dtype), _need(ids, "ids", torch.int32)
+    n, W = h.shape
+    if out.dtype not in DT_CODE or tuple(out.shape) != (n, 2 * W) or table.shape[1] != W or ids.numel() != n:
+        raise KernelError("concat_stream_rows: shapes or dtype do not agree")
+    f = _fn("stream_ops.cu", "dli_concat_stream_rows", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(h), _ptr(table), _ptr(ids), n, W, DT_CODE[out.dtype], _stream()), "concat_stream_rows")
+
+
+def token_shift_blend(out: torch.Tensor, x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, seq_of_token: torch.Tensor, q_start: torch.Tensor,
+                      state_slot: torch.Tensor) -> None:
+    """out[j, t] = x[t] + (before(t) - x[t]) * mu[j]: ``mu`` [blends, W] float32; before(t) is the row of the token in front of t in its
+    sequence — x[t - 1] inside the step, the sequence's carried row ``state`` [slots, 1, W] at the step's first token.
+    ``conv_state_update`` (one carried row) moves the state on afterwards."""
+    _need(out, "out"), _need(x, "x", out.dtype), _need(mu, "mu", torch.float32), _need(state, "state", out.dtype)
+    _need(seq_of_token, "seq_of_token", torch.int32), _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    n, W = x.shape
+    blends = mu.shape[0]
+    if out.dtype not in DT_CODE or tuple(out.shape) != (blends, n, W) or mu.shape[1] != W or tuple(state.shape[1:]) != (1, W) or seq_of_token.numel() != n:
+        raise KernelError("token_shift_blend: shapes or dtype do not agree")
+    f = _fn("stream_ops.cu", "dli_token_shift_blend", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(x), _ptr(mu), _ptr(state), _ptr(seq_of_token), _ptr(q_start), _ptr(state_slot), n, W, blends, DT_CODE[out.dtype], _stream()),
+           "token_shift_blend")
+
+
+# ------------------------------------------------------------------ recurrences whose state decays per head and key channel
+
+RECURRENCE_MAX_HEAD_DIM = 512
+
+
+def decay_recurrence_row(kq_heads: int, heads: int, d: int, dv: int) -> int:
+    """Floats of a token's row as ``decay_recurrence`` reads it: A [kq_heads, d] (what the state is read with) | K [kq_heads, d] |
+    G [heads, d] (decays) | V [heads, dv] | B [heads] (betas), rounded up to a multiple of 4 (csrc/recurrence.cu: row_layout)."""
+    return (2 * kq_heads * d + heads * d + heads * dv + heads + 3) & ~3
+
+
+def shift_decay_prep(rows: torch.Tensor, rkvg: torch.Tensor, wz: torch.Tensor, w0: torch.Tensor, heads: int, d: int) -> None:
+    """The float32 rows of the token-shift recurrence: A = r, K = k, V = v (slabs 0, 1, 2 of ``rkvg`` [4, n, heads d]) and the decays
+    G = exp(-exp(wz + w0)) (``wz`` [n, heads d], ``w0`` [heads d] float32)."""
+    _need(rows, "rows", torch.float32), _need(rkvg, "rkvg"), _need(wz, "wz", rkvg.dtype), _need(w0, "w0", torch.float32)
+    n, I = wz.shape
+    if rkvg.dtype not in DT_CODE or I != heads * d or tuple(rkvg.shape) != (4, n, I) or w0.numel() != I or tuple(rows.shape) != (n, decay_recurrence_row(heads, heads, d, d)):
+        raise KernelError("shift_decay_prep: shapes or dtype do not agree")
+    f = _fn("recurrence.cu", "dli_shift_decay_prep", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(rows), _ptr(rkvg), _ptr(wz), _ptr(w0), n, heads, d, DT_CODE[rkvg.dtype], _stream()), "shift_decay_prep")
+
+
+def channel_delta_prep(rows: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b_col: int, a: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                       heads: int, kv_heads: int, d: int, dv: int, unit_eps: float) -> None:
+    """The float32 rows of the delta rule with a decay per channel.  qkv [n, 2 kv_heads d + heads dv]: q | k | v after convolution and
+    activation; q and k become unit vectors per head (``unit_eps`` inside the root), q also times d^-1/2; B = sigmoid(u[:, b_col + h]);
+    G = exp(-exp(a_log[h]) softplus(a[:, h d + i] + dt_bias[h d + i]))."""
+    _columns(u, "channel_delta_prep"), _need(rows, "rows", torch.float32), _need(qkv, "qkv", u.dtype), _need(a, "a", u.dtype)
+    _need(dt_bias, "dt_bias", torch.float32), _need(a_log, "a_log", torch.float32)
+    n = qkv.shape[0]
+    if (kv_heads < 1 or heads % kv_heads or qkv.shape[1] != 2 * kv_heads * d + heads * dv or tuple(a.shape) != (n, heads * d) or u.shape[0] != n
+            or b_col + heads > u.shape[1] or dt_bias.numel() != heads * d or a_log.numel() != heads
+            or tuple(rows.shape) != (n, decay_recurrence_row(kv_heads, heads, d, dv))):
+        raise KernelError("channel_delta_prep: shapes do not agree")
+    f = _fn("recurrence.cu", "dli_channel_delta_prep", [c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 5
+            + [c_float, c_int, c_void_p])
+    _check(f(_ptr(rows), _ptr(qkv), _ptr(u), u.stride(0), b_col, _ptr(a), _ptr(dt_bias), _ptr(a_log), n, heads, kv_heads, d, dv, unit_eps,
+             DT_CODE[u.dtype], _stream()), "channel_delta_prep")
+
+
+def decay_recurrence(o: torch.Tensor, rows: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, kq_heads: int,
+                     mode: str, bonus: torch.Tensor | None = None, max_len: int = 1 << 30) -> None:
+    """A linear recurrence over every sequence's tokens of this step, from and to its slot of ``state`` [slots, heads, dv, d] (float32; S
+    transposed, so that a value column's d numbers are contiguous).  ``rows`` [n, decay_recurrence_row(...)] float32.  Per head, with
+    a, k (of q/k head h // (heads / kq_heads)), decays g [d], values v [dv]:
+
+    ``"bonus"``:  o = (S + diag(u) k v^T)^T a;   S <- diag(g) S + k v^T          (``bonus`` [heads, d]: u)
+    ``"delta"``:  S <- diag(g) S;   w = beta (v - S^T k);   S <- S + k w^T;   o = S^T a
+
+    o [n, heads dv] float32.  Tokens are walked in order, the sums over d added in an order the sizes fix."""
+    _need(o, "o", torch.float32), _need(rows, "rows", torch.float32), _need(state, "state", torch.float32)
+    _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
+    _, heads, dv, d = state.shape
+    n = rows.shape[0]
+    if mode not in ("bonus", "delta") or (mode == "bonus") != (bonus is not None):
+        raise KernelError("decay_recurrence: mode is bonus (with its vector) or delta")
+    if bonus is not None:
+        _need(bonus, "bonus", torch.float32)
+        if tuple(bonus.shape) != (heads, d):
+            raise KernelError("decay_recurrence: bonus must be [heads, d]")
+    if (kq_heads < 1 or heads % kq_heads or d > RECURRENCE_MAX_HEAD_DIM or tuple(o.shape) != (n, heads * dv) or rows.shape[1] != decay_recurrence_row(kq_heads, heads, d, dv)
+            or q_start.numel() != state_slot.numel() + 1):
+        raise KernelError(f"decay_recurrence: shapes do not agree (or the head size is above {RECURRENCE_MAX_HEAD_DIM})")
+    f = _fn("recurrence.cu", "dli_decay_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    _check(f(_ptr(o), _ptr(rows), _ptr(state), _ptr(q_start), _ptr(state_slot), _ptr(bonus), state_slot.numel(), heads, kq_heads, d, dv,
+             0 if mode == "bonus" else 1, _stream()), "decay_recurrence")
+
+
+# ------------------------------------------------------------------ routed mixture of gated feed-forwards
+
+MOE_MAX_TOP = 32
+MOE_PAIR_CHUNK = 8192  # tokens a launch of the pair kernels takes (their grids count (token, expert) pairs along y)
+
+
+def moe_route(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, group_count: int,
+              group_keep: int, scale: float) -> None:
+    """Which experts every token uses, and with what weights.  z = x router^T (float32), s = sigmoid(z), choice = s + correction.
+    With ``group_count`` > 1 the experts form equal groups of neighbours, a group's mark is the sum of its two largest choice scores,
+    and only experts of the ``group_keep`` best groups are eligible.  ids [n, top] int32: the eligible experts with the largest choice
+    scores, best first (ties: the lower index); weights [n, top] float32 = s[ids] / (their sum + 1e-20) * scale."""
+    _need(ids, "ids", torch.int32), _need(weights, "weights", torch.float32), _need(x, "x"), _need(router, "router", torch.float32)
+    _need(correction, "correction", torch.float32)
+    n, W = x.shape
+    E, top = router.shape[0], ids.shape[1]
+    if (x.dtype not in DT_CODE or router.shape[1] != W or correction.numel() != E or tuple(ids.shape) != (n, top) or tuple(weights.shape) != (n, top)
+            or top > MOE_MAX_TOP or group_count < 1 or E % group_count or not 1 <= group_keep <= group_count or top > group_keep * (E // group_count)):
+        raise KernelError("moe_route: shapes, dtype or groups do not agree")
+    f = _fn("moe.cu", "dli_moe_route", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_float, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(weights), _ptr(x), _ptr(router), _ptr(correction), n, W, E, top, group_count, group_keep, float(scale), DT_CODE[x.dtype],
+             _stream()), "moe_route")
+
+
+def moe_experts(out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                activation: str = "silu") -> None:
+    """out[t] = sum_k weights[t, k] * down_e(act(gate_e x[t]) * (up_e x[t])), e = ids[t, k], added in the order of k in float32.
+    w_gate_up [E, 2 ff, W] (an expert's gate rows, then its up rows), w_down [E, W, ff].  The two inner sums are rounded to the
+    activation dtype before the activation, and so is their product."""
+    _need(out, "out"), _need(x, "x", out.dtype), _need(ids, "ids", torch.int32), _need(weights, "weights", torch.float32)
+    _need(w_gate_up, "w_gate_up", out.dtype), _need(w_down, "w_down", out.dtype)
+    n, W = x.shape
+    top = ids.shape[1]
+    E, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    if (out.dtype not in DT_CODE or tuple(out.shape) != (n, W) or w_gate_up.shape[2] != W or tuple(w_down.shape) != (E, W, ff) or tuple(ids.shape) != (n, top)
+            or tuple(weights.shape) != (n, top) or activation not in GLU_ACTIVATIONS):
+        raise KernelError("moe_experts: shapes, dtype or activation do not agree")
+    f = _fn("moe.cu", "dli_moe_pairs", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    step = max(1, min(MOE_PAIR_CHUNK, 65535 // top))
+    hidden = torch.empty((min(n, step) * top, ff), dtype=out.dtype, device=out.device)
+    global launch_count
+    for t0 in range(0, n, step):
+        m = min(step, n - t0)
+        _check(f(_ptr(out[t0:]), _ptr(hidden), _ptr(x[t0:]), _ptr(ids[t0:]), _ptr(weights[t0:]), _ptr(w_gate_up), _ptr(w_down), m, W, ff, top,
+                 GLU_ACTIVATIONS[activation], DT_CODE[out.dtype], _stream()), "moe_experts")
+        launch_count += 1  # two kernels a call

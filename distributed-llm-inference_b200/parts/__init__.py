@@ -1,4 +1,4 @@
-from . import attention, block, entry, mlp, model, norm, rotary, ssm  # noqa: F401  (registers the parts)
+from . import attention, block, entry, mlp, model, norm, pair, rotary, ssm  # noqa: F401  (registers the parts)
 from .base import BuildEnv, Part, ResidualStream, build_part, register_part, unregister_part
 from .model import DecoderModel, declared_tensors
 

@@ -9,7 +9,8 @@ import torch
 from ..cache.needs import PagedKVNeed
 from ..kernels import attention as attn_kernels
 from ..kernels import ops
-from ..kernels.gemm import heads_product, last_product, project
+from ..cache.needs import StateNeed
+from ..kernels.gemm import heads_product, last_product, project, project_bias
 from ..weights.loader import TensorDecl
 from .base import Part, build_part, register_part, tensor_name
 
@@ -169,6 +170,103 @@ class SinkAttention(Part):
         return project(out, self.wo)
 
 
+@register_part("mixer", "conv_attention")
+class ConvAttention(Part):
+    """Causal grouped-query softmax attention whose q, k and v pass a short causal convolution over time right after their
+    projections, with options other designs can switch:
+
+    * ``bias``: q, k, v and the output projection have biases (added in the projection, before the convolution);
+    * ``conv_taps``: taps of the per-channel convolution without bias or activation (1: a scale per channel); a request
+      keeps the last taps - 1 projected rows in its state slot;
+    * ``rotary_dim`` / ``theta``: rotate-half rotation of the first rotary_dim dimensions of every q and k head;
+    * ``qk_unit_eps`` (or None): AFTER the rotation every q and k head is divided by its root mean square (no weight);
+    * ``value_dim``: the values' size may differ from the keys'.  Pages hold rows of max(head_dim, value_dim) numbers, the
+      shorter of keys and values padded with zeros, so every attention kernel of the engine serves; the output
+      projection's matrix is padded with zero columns to match, once, at load.
+
+    One product yields q | k | v; one kernel convolves; one kernel rotates, norms and writes the pages.
+    params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim, conv_taps, scale, window, bias, qk_unit_eps, rotary_dim,
+    theta, tensors (names of q, k, v, o, q_bias, k_bias, v_bias, o_bias, q_conv, k_conv, v_conv)."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.d = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.dv = int(p.get("value_dim") or self.d)
+        self.row = max(self.d, self.dv)  # what a page keeps per token and KV head, for keys and for values
+        self.taps = int(p.get("conv_taps") or 1)
+        self.scale = float(p["scale"])
+        self.window = p.get("window")
+        self.bias = bool(p.get("bias", False))
+        self.unit_eps = None if p.get("qk_unit_eps") is None else float(p["qk_unit_eps"])
+        self.rotary_dim = int(p.get("rotary_dim") or 0)
+        if self.nh % self.nkv or self.rotary_dim % 2 or self.rotary_dim > self.d or self.taps < 1:
+            raise ValueError("conv_attention: num_heads must be a multiple of num_kv_heads, rotary_dim even and at most head_dim, conv_taps >= 1")
+        self.inv_freq = None
+        if self.rotary_dim:
+            from .rotary import inverse_frequencies
+
+            self.inv_freq = inverse_frequencies({"rotary_dim": self.rotary_dim, "theta": float(p["theta"])}).to(env.device)
+        defaults = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight", "q_bias": "q_proj.bias",
+                    "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias", "q_conv": "q_conv.weight", "k_conv": "k_conv.weight",
+                    "v_conv": "v_conv.weight"}
+        self.names = {role: tensor_name(spec, role, default) for role, default in defaults.items()}
+        self.sizes = {"q": self.nh * self.d, "k": self.nkv * self.d, "v": self.nkv * self.dv}
+        self.channels = sum(self.sizes.values())
+        self.w_in = self.b_in = self.w_conv = self.wo = self.bo = None
+
+    def declare(self):
+        nm, H = self.names, self.hidden
+        out = {nm["o"]: TensorDecl((H, self.nh * self.dv))}
+        for role, size in self.sizes.items():
+            out[nm[role]] = TensorDecl((size, H))
+            out[nm[role + "_conv"]] = TensorDecl((size, self.taps), "vector32")
+            if self.bias:
+                out[nm[role + "_bias"]] = TensorDecl((size,))
+        if self.bias:
+            out[nm["o_bias"]] = TensorDecl((H,))
+        return out
+
+    def load(self, tensors):
+        nm = self.names
+        self.w_in = torch.cat([tensors[nm[r]] for r in ("q", "k", "v")], 0).contiguous()
+        self.w_conv = torch.cat([tensors[nm[r + "_conv"]] for r in ("q", "k", "v")], 0).t().contiguous()  # [taps, channels]
+        wo = tensors[nm["o"]]
+        if self.row != self.dv:  # the attention kernels leave rows of ``row`` numbers per head: zero columns where the padding lies
+            padded = torch.zeros((self.hidden, self.nh, self.row), dtype=wo.dtype, device=wo.device)
+            padded[:, :, : self.dv] = wo.view(self.hidden, self.nh, self.dv)
+            wo = padded.view(self.hidden, self.nh * self.row)
+        self.wo = wo.contiguous()
+        if self.bias:
+            self.b_in = torch.cat([tensors[nm[r + "_bias"]] for r in ("q", "k", "v")], 0).contiguous()
+            self.bo = tensors[nm["o_bias"]]
+
+    def cache_need(self):
+        return (PagedKVNeed(self.nkv, self.row, self.window), StateNeed((self.taps - 1, self.channels), self.env.dtype))
+
+    def decode_launch_key(self, num_seqs: int, max_kv_len: int, page_size: int):
+        return attn_kernels.decode_splits(num_seqs, self.nh, self.nkv, self.row, page_size, max_kv_len)
+
+    def forward(self, x: torch.Tensor, batch, cache) -> torch.Tensor:
+        n = x.shape[0]
+        conv_state = cache.states[0]
+        proj = project_bias(x, self.w_in, self.b_in)
+        mixed = torch.empty((n, self.channels), dtype=x.dtype, device=x.device)
+        ops.causal_conv_silu(mixed, proj, 0, self.w_conv, None, conv_state, batch.seq_of_token, batch.q_start, batch.state_slot, activation=False)
+        if self.taps > 1:
+            ops.conv_state_update(conv_state, proj, 0, batch.q_start, batch.state_slot)
+        group = batch.group(cache.group)
+        q = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
+        ops.rotary_unit_store(q, mixed, batch.positions, self.inv_freq, group.slots if cache.writes else None, cache.k if cache.writes else None,
+                              cache.v if cache.writes else None, self.nh, self.nkv, self.d, self.dv, self.rotary_dim, self.unit_eps, cache.page_size)
+        out = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
+        attn_kernels.paged_attention(out, q, cache, batch, self.nh, self.scale, self.window, splits=batch.launch_keys.get(id(self)))
+        return project_bias(out, self.wo, self.bo)
+
+
 @register_part("mixer", "latent_attention")
 class LatentAttention(Part):
     """Attention whose keys and values are both made from one small cached vector per token (a latent).
@@ -187,9 +285,16 @@ class LatentAttention(Part):
 
     One product yields q | down | g; one kernel norms the latent, rotates, writes the cache row and places the rotated
     query parts behind the latent-space queries.
+    ``rotary_pairing``: ``"half"`` (dimension i turns with i + rotary_dim / 2) or ``"neighbours"`` (2i with 2i + 1).  A
+    score only sees the rotated parts through their dot product, so for neighbouring pairs the rows of W_q's and W_dkv's
+    rotated parts are put into the half layout once, at load, and the same kernel serves both.  ``rotary_scaling`` (factor,
+    original, fast, slow): YaRN frequencies and the factor on cosines and sines (``paired_rotary_frequencies``).
+    ``head_sinks``: a learned score per head (tensor ``sink``) whose exponential joins every softmax denominator of that
+    head and carries no value.
+
     params: hidden_size, num_heads, head_dim, rot_dim, value_dim, kv_rank, scale, window, gate, eps, rotary_dim (how
-    many of the rot_dim dimensions are rotated, rotate-half pairing), theta, tensors (names of q, dkv, dkv_norm, uk,
-    uv, g, o)."""
+    many of the rot_dim dimensions are rotated), theta, rotary_pairing, rotary_scaling, head_sinks, tensors (names of q,
+    dkv, dkv_norm, uk, uv, g, o, sink)."""
 
     graph_capturable = True
     takes_scaled_rows = False
@@ -209,13 +314,22 @@ class LatentAttention(Part):
             raise ValueError(f"rotary_dim={self.rotary_dim} must be even and at most rot_dim={self.dr}")
         self.row = self.rank + self.dr  # what a token keeps in the cache, and the size of a query in the latent space
         self.inv_freq = None
-        if self.rotary_dim:
+        self.amp = 1.0
+        self.pairing = p.get("rotary_pairing", "half")
+        if self.pairing not in ("half", "neighbours"):
+            raise ValueError(f"rotary_pairing={self.pairing!r} (half, neighbours)")
+        if self.rotary_dim and (p.get("rotary_scaling") or self.pairing == "neighbours"):
+            freq, self.amp = paired_rotary_frequencies(self.rotary_dim, float(p["theta"]), p.get("rotary_scaling"))
+            self.inv_freq = torch.tensor(freq, dtype=torch.float64).to(torch.float32).to(env.device)
+        elif self.rotary_dim:
             from .rotary import inverse_frequencies
 
             self.inv_freq = inverse_frequencies({"rotary_dim": self.rotary_dim, "theta": float(p["theta"])}).to(env.device)
+        self.head_sinks = bool(p.get("head_sinks", False))
+        self.sinks = None
         self.names = {role: tensor_name(spec, role, default) for role, default in (
             ("q", "q_proj.weight"), ("dkv", "kv_down_proj.weight"), ("dkv_norm", "kv_norm.weight"), ("uk", "k_up_proj.weight"),
-            ("uv", "v_up_proj.weight"), ("g", "g_proj.weight"), ("o", "o_proj.weight"))}
+            ("uv", "v_up_proj.weight"), ("g", "g_proj.weight"), ("o", "o_proj.weight"), ("sink", "sinks"))}
         self.q_cols = self.nh * (self.d + self.dr)
         self.gate_col = self.q_cols + self.row
         self.w_in = self.w_uk = self.w_uv = self.wo = self.w_norm = None
@@ -227,11 +341,29 @@ class LatentAttention(Part):
                nm["uv"]: TensorDecl((self.nh * self.dv, self.rank)), nm["o"]: TensorDecl((H, self.nh * self.dv))}
         if self.gated:
             out[nm["g"]] = TensorDecl((self.nh * self.dv, H))
+        if self.head_sinks:
+            out[nm["sink"]] = TensorDecl((self.nh,), "vector32")
         return out
+
+    def _half_layout(self, w: torch.Tensor, heads: int, plain: int) -> torch.Tensor:
+        """Rows of a projection whose heads are [plain | rot_dim]: the first rotary_dim rows of every rotated part, stored as
+        neighbouring pairs (2i, 2i + 1), reordered to evens then odds, so that pair i sits at (i, i + rotary_dim / 2)."""
+        r = self.rotary_dim
+        order = torch.cat([torch.arange(0, r, 2), torch.arange(1, r, 2), torch.arange(r, self.dr)]).to(w.device)
+        per = plain + self.dr
+        v = w.view(heads, per, w.shape[1]).clone()
+        v[:, plain:] = v[:, plain:][:, order]
+        return v.view(heads * per, w.shape[1])
 
     def load(self, tensors):
         nm = self.names
-        rows = [tensors[nm["q"]], tensors[nm["dkv"]]] + ([tensors[nm["g"]]] if self.gated else [])
+        wq, wd = tensors[nm["q"]], tensors[nm["dkv"]]
+        if self.pairing == "neighbours" and self.rotary_dim:
+            wq = self._half_layout(wq, self.nh, self.d)
+            wd = torch.cat([wd[: self.rank], self._half_layout(wd[self.rank :], 1, 0)], 0)
+        rows = [wq, wd] + ([tensors[nm["g"]]] if self.gated else [])
+        if self.head_sinks:
+            self.sinks = tensors[nm["sink"]]
         self.w_in = torch.cat(rows, 0).contiguous()
         self.w_uk = tensors[nm["uk"]].view(self.nh, self.d, self.rank)  # q_latent[a] = q_plain[a] W_uk[a]
         self.w_uv = tensors[nm["uv"]].view(self.nh, self.dv, self.rank).transpose(1, 2).contiguous()  # o[a] = o_latent[a] W_uv[a]^T
@@ -250,11 +382,12 @@ class LatentAttention(Part):
         # the latent-space queries [n, heads, kv_rank + rot_dim]: the kernel fills the rotated tails, the product the rest
         q = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
         ops.latent_prep(q, proj, self.w_norm, self.eps, batch.positions, self.inv_freq, group.slots if cache.writes else None,
-                        cache.k if cache.writes else None, self.nh, self.d, self.dr, self.rank, self.rotary_dim, cache.page_size)
+                        cache.k if cache.writes else None, self.nh, self.d, self.dr, self.rank, self.rotary_dim, cache.page_size, amp=self.amp)
         heads_product(proj[:, : self.q_cols].view(n, self.nh, self.d + self.dr)[:, :, : self.d], self.w_uk,
                       q.view(n, self.nh, self.row)[:, :, : self.rank])
         latent = torch.empty((n, self.nh * self.row), dtype=x.dtype, device=x.device)
-        attn_kernels.paged_attention(latent, q, cache, batch, self.nh, self.scale, self.window, splits=batch.launch_keys.get(id(self)))
+        attn_kernels.paged_attention(latent, q, cache, batch, self.nh, self.scale, self.window, splits=batch.launch_keys.get(id(self)),
+                                     sink=self.sinks)
         out = torch.empty((n, self.nh * self.dv), dtype=x.dtype, device=x.device)
         heads_product(latent.view(n, self.nh, self.row)[:, :, : self.rank], self.w_uv, out.view(n, self.nh, self.dv),
                       gate=proj[:, self.gate_col : self.gate_col + self.nh * self.dv] if self.gated else None)

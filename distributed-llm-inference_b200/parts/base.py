@@ -45,6 +45,9 @@ these is served with plain tensors:
 * an arrangement with ``first_consumer() -> (norm, part)`` and ``defer_last_product(flag)`` lets
   the model extend this across layer borders.
 
+A sublayer output with a learned scale per feature stays pending as ``PendingScaled``; a norm with
+``takes_pending_scaled`` multiplies and adds it in its own kernel, any other reader has it settled first.
+
 The outputs of two branches that run side by side stay pending as ``PendingSum(a, b)``; a norm with
 ``takes_pending_sum`` adds both in its own kernel, any other reader has them settled first.
 
@@ -142,6 +145,36 @@ class PendingSum:
         return self.a.float() if self.b is None else self.a.float() + self.b.float()
 
 
+class WeightedPair:
+    """What a mixer made of two mixers side by side returns: fa * a + fb * b, not yet added up (a, b in the activation
+    dtype).  Whoever adds it to the stream does the sum in float32."""
+
+    __slots__ = ("a", "fa", "b", "fb")
+
+    def __init__(self, a: torch.Tensor, fa: float, b: torch.Tensor, fb: float) -> None:
+        self.a, self.fa, self.b, self.fb = a, float(fa), b, float(fb)
+
+
+class PendingScaled:
+    """A sublayer output that is still to be multiplied, feature by feature, by a learned float32 vector ``scale`` and
+    added to the residual stream: h += scale * (fa * a + fb * b) with b absent for a plain tensor.  A norm with
+    ``takes_pending_scaled`` does it in its own kernel."""
+
+    __slots__ = ("a", "fa", "b", "fb", "scale")
+
+    def __init__(self, out, scale: torch.Tensor) -> None:
+        if isinstance(out, WeightedPair):
+            self.a, self.fa, self.b, self.fb = out.a, out.fa, out.b, out.fb
+        else:
+            self.a, self.fa, self.b, self.fb = out, 1.0, None, 0.0
+        self.scale = scale
+
+    def add_into(self, h: torch.Tensor) -> None:
+        from ..kernels import ops
+
+        ops.add_rmsnorm_scaled(None, h, self.a, self.fa, self.b, self.fb, self.scale, None, 0.0)
+
+
 class ResidualStream:
     """The float32 residual h [n, H] and a delta (activation dtype) not yet added to it.
     Keeping the delta pending lets the next norm do the addition in the same kernel.  ``pending``
@@ -182,6 +215,8 @@ class ResidualStream:
             delta.norm.add_into(self.h, delta.a)
         elif isinstance(delta, PendingSum):
             self.h += delta.total()
+        elif isinstance(delta, PendingScaled):
+            delta.add_into(self.h)
         elif delta is not None:
             self.h += (delta.materialize() if isinstance(delta, PendingProduct) else delta).float()
         return self.h
@@ -206,6 +241,11 @@ def normed_input(norm, h: torch.Tensor, delta, consumer, rows: torch.Tensor | No
         delta = None
     if isinstance(delta, PendingSum) and not getattr(norm, "takes_pending_sum", False):
         h += delta.total()
+        delta = None
+    if isinstance(delta, PendingScaled) and not getattr(norm, "takes_pending_scaled", False):
+        if rows is not None:
+            raise TypeError("a scaled delta that is still pending can only be read row by row by a norm that takes it")
+        delta.add_into(h)
         delta = None
     if isinstance(delta, PendingProduct):
         if rows is None and can_fuse(norm, consumer):

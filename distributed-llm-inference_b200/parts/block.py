@@ -4,7 +4,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import BuildEnv, Part, PendingNormed, PendingSum, ResidualStream, build_part, can_fuse, normed_input, register_part
+from ..weights.loader import TensorDecl
+from .base import BuildEnv, Part, PendingNormed, PendingScaled, PendingSum, ResidualStream, build_part, can_fuse, normed_input, register_part
 
 
 @register_part("arrangement", "prenorm")
@@ -46,6 +47,49 @@ class PreNormBlock(Part):
         a = self.mixer.forward(y, batch, cache)
         y = normed_input(self.ffn_norm, stream.h, a, self.ffn)
         stream.pending = self.ffn.forward(y)
+
+
+@register_part("arrangement", "prenorm_scaled")
+class ScaledPreNormBlock(Part):
+    """x <- x + s1 * mixer(norm(x)); x <- x + s2 * ffn(norm(x)): pre-norm with a learned float32 scale per feature on each
+    sublayer's output (s1, s2: tensors of the arrangement itself, named by the layer's ``mixer_scale`` and ``ffn_scale``).
+    Roles: mixer_norm, mixer, and — a layer may have no feed-forward — ffn_norm, ffn.  A sublayer's output stays pending
+    with its scale (``PendingScaled``), so the next norm multiplies, adds and norms in one kernel; a mixer may return a
+    ``WeightedPair`` (two mixers side by side), whose sum is formed in that kernel as well."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env: BuildEnv) -> None:
+        self.spec, self.env = spec, env
+        self.size = int(spec.params["size"])
+        self.mixer_norm = build_part("norm", spec.parts["mixer_norm"], env)
+        self.mixer = build_part("mixer", spec.parts["mixer"], env)
+        self.has_ffn = "ffn" in spec.parts
+        if self.has_ffn:
+            self.ffn_norm = build_part("norm", spec.parts["ffn_norm"], env)
+            self.ffn = build_part("feed_forward", spec.parts["ffn"], env)
+        self.names = [spec.params["mixer_scale"]] + ([spec.params["ffn_scale"]] if self.has_ffn else [])
+        self.scales: list[torch.Tensor] = []
+
+    def children(self):
+        return [self.mixer_norm, self.mixer] + ([self.ffn_norm, self.ffn] if self.has_ffn else [])
+
+    def declare(self):
+        return {name: TensorDecl((self.size,), "vector32") for name in self.names}
+
+    def load(self, tensors):
+        self.scales = [tensors[name] for name in self.names]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, stream: ResidualStream, batch, cache) -> None:
+        y = normed_input(self.mixer_norm, stream.h, stream.take_pending(), self.mixer)
+        pending = PendingScaled(self.mixer.forward(y, batch, cache), self.scales[0])
+        if self.has_ffn:
+            y = normed_input(self.ffn_norm, stream.h, pending, self.ffn)
+            pending = PendingScaled(self.ffn.forward(y), self.scales[1])
+        stream.pending = pending
 
 
 @register_part("arrangement", "sandwich")

@@ -130,3 +130,34 @@ class DepthAverage(Part):
         y = torch.empty(out.shape, dtype=self.env.dtype, device=out.device) if want_cast and self.env.dtype != torch.float32 else None
         ops.depth_average(out, x0, hist, self.weight, self.index + 2, y)
         stream.h, stream.cast = out, y
+
+
+@register_part("stream_entry", "concat_project")
+class ConcatProject(Part):
+    """What a looped span of layers does to the stream before one of its passes: x <- W [x; x0], a product that reads the
+    stream and the embedding output x0 side by side (W [size, 2 size], the stream's columns first).  x0 is gathered again
+    from the embedding table by the step's token ids, so no copy of it is kept across the layers; one kernel lays
+    [x; x0] out in the activation dtype, and the product's float32 sums become the new stream.
+    params: size, vocab_size, table (the embedding tensor's name), tensor (W's name)."""
+
+    graph_capturable = True
+
+    def __init__(self, spec, env) -> None:
+        super().__init__(spec, env)
+        p = spec.params
+        self.size, self.vocab = int(p["size"]), int(p["vocab_size"])
+        self.table_name, self.name = p["table"], tensor_name(spec, "weight", "weight")
+        self.table = self.weight = None
+
+    def declare(self):
+        return {self.table_name: TensorDecl((self.vocab, self.size)), self.name: TensorDecl((self.size, 2 * self.size))}
+
+    def load(self, tensors):
+        self.table, self.weight = tensors[self.table_name], tensors[self.name]
+
+    def apply(self, stream: ResidualStream, batch) -> None:
+        h = stream.settle()
+        both = torch.empty((h.shape[0], 2 * self.size), dtype=self.env.dtype, device=h.device)
+        ops.concat_stream_rows(both, h, self.table, batch.token_ids)
+        stream.h = project(both, self.weight, out_dtype=torch.float32)
+        stream.cast = None

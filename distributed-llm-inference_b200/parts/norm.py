@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Part, PendingSum, register_part, tensor_name
+from .base import Part, PendingScaled, PendingSum, register_part, tensor_name
 
 
 @register_part("norm", "rmsnorm")
@@ -17,11 +17,13 @@ class RMSNorm(Part):
     offset (added to the stored weight at load: 1.0 for checkpoints that store the deviation from one).
 
     ``delta`` may be a ``PendingSum`` of two sublayer outputs (layers whose branches run side by side): both are
-    added in the same kernel.  ``add_norm_pair`` also norms the same sum with a second norm's weight — two readers
+    added in the same kernel.  It may be a ``PendingScaled`` (one or two outputs with constant factors and a learned
+    scale per feature): multiplied and added in the same kernel too.  ``add_norm_pair`` also norms the same sum with a second norm's weight — two readers
     of one stream share the sum of squares."""
 
     graph_capturable = True
     takes_pending_sum = True
+    takes_pending_scaled = True
 
     def __init__(self, spec, env) -> None:
         super().__init__(spec, env)
@@ -45,6 +47,8 @@ class RMSNorm(Part):
         y = self._out(h, rows)
         if isinstance(delta, PendingSum):
             ops.add_rmsnorm_pair(y, None, h, delta.a, delta.b, self.weight, None, self.eps, rows)
+        elif isinstance(delta, PendingScaled):
+            ops.add_rmsnorm_scaled(y, h, delta.a, delta.fa, delta.b, delta.fb, delta.scale, self.weight, self.eps, rows)
         else:
             ops.add_rmsnorm(y, h, delta, self.weight, self.eps, rows)
         return y

@@ -27,7 +27,7 @@ class CheckpointError(ValueError):
 
 @dataclass(frozen=True)
 class TensorDecl:
-    shape: tuple[int, ...]
+    shape: tuple[int | None, ...]  # None: a size that only the checkpoint gives (the inner size of a low-rank product)
     kind: str = "matrix"  # "matrix" | "vector32" | "int"
     # name of another declared tensor this one must equal if the file stores it anyway
     # (a tied head some checkpoints serialise): the duplicate is checked and dropped
@@ -74,7 +74,9 @@ def load_tensors(
     wrong = []
     for name in sorted(expected.keys() & where.keys()):
         got = where[name].entries[name].shape
-        if tuple(got) != tuple(expected[name].shape):
+        want = tuple(expected[name].shape)
+        # a size the model leaves open (None) is whatever the file holds: it is given by no key of config.json
+        if len(got) != len(want) or any(w is not None and int(g) != w for g, w in zip(got, want)):
             wrong.append(f"{name}: file {list(got)}, model {list(expected[name].shape)}")
     if missing or unexpected or wrong:
         raise CheckpointError(

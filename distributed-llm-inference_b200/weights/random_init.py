@@ -39,6 +39,8 @@ def random_tensors(
         if decl.optional_alias_of:
             continue
         g = _generator(seed, name, device)
+        if any(d is None for d in decl.shape):
+            raise ValueError(f"{name}: a size of {list(decl.shape)} is left to the checkpoint; random weights need it in the configuration")
         if decl.kind == "matrix":
             t = torch.empty(decl.shape, dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=g).to(dtype)
         elif decl.kind == "vector32":

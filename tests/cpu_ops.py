@@ -120,7 +120,9 @@ def paged_attention_simt(out, qkv, k_pool, v_pool, block_tables, seq_of_token, p
         v = v_pool[pages, :, (keys % page_size).long(), :].float()
         k, v = k.repeat_interleave(fan, 1), v.repeat_interleave(fan, 1)  # [keys, nh, d]
         s = torch.einsum("hd,khd->hk", q[t], k) * scale
-        if sink is not None:  # one more term in the denominator, without a value
+        if isinstance(sink, torch.Tensor):  # a learned score per head
+            s = torch.cat([s, sink.float().view(num_heads, 1)], -1)
+        elif sink is not None:  # one more term in the denominator, without a value
             s = torch.cat([s, torch.full((num_heads, 1), float(sink))], -1)
         w = torch.softmax(s, -1)[:, : keys.numel()]
         out[t] = torch.einsum("hk,khd->hd", w, v).reshape(-1).to(out.dtype)
@@ -193,6 +195,8 @@ def activation(x, kind):
         z = torch.relu(z) ** 2
     elif kind == "gelu_tanh":
         z = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z**3)))
+    elif kind == "tanh":
+        z = torch.tanh(z)
     else:
         z = z / (1 + torch.exp(-z))
     x.copy_(z.to(x.dtype))
@@ -226,7 +230,7 @@ def qk_norm_rotary_store(proj, wq, wk, eps, positions, inv_freq, slots, k_pool, 
     return qk[:, :num_heads].reshape(n, nq).to(proj.dtype)
 
 
-def latent_prep(q_out, proj, w_norm, eps, positions, inv_freq, slots, k_pool, num_heads, head_dim, rot_dim, kv_rank, rotary_dim, page_size):
+def latent_prep(q_out, proj, w_norm, eps, positions, inv_freq, slots, k_pool, num_heads, head_dim, rot_dim, kv_rank, rotary_dim, page_size, amp=1.0):
     n = proj.shape[0]
     qc = num_heads * (head_dim + rot_dim)
     down = proj[:, qc : qc + kv_rank + rot_dim].float()
@@ -236,7 +240,7 @@ def latent_prep(q_out, proj, w_norm, eps, positions, inv_freq, slots, k_pool, nu
     if rotary_dim:
         half = rotary_dim // 2
         ang = positions.float()[:, None] * inv_freq[None, :]
-        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        cos, sin = ang.cos()[:, None, :] * amp, ang.sin()[:, None, :] * amp
         lo, hi = turn[..., :half].clone(), turn[..., half:rotary_dim].clone()
         turn[..., :half] = lo * cos - hi * sin
         turn[..., half:rotary_dim] = hi * cos + lo * sin
@@ -264,7 +268,7 @@ def _silu(x):
     return x / (1 + torch.exp(-x))
 
 
-def causal_conv_silu(out, u, col0, weight, bias, state, seq_of_token, q_start, state_slot):
+def causal_conv_silu(out, u, col0, weight, bias, state, seq_of_token, q_start, state_slot, activation=True):
     n, C = out.shape
     taps = weight.shape[0]  # weight [taps, C]
     for t in range(n):
@@ -275,7 +279,7 @@ def causal_conv_silu(out, u, col0, weight, bias, state, seq_of_token, q_start, s
             r = t - first - (taps - 1) + j
             x = u[first + r, col0 : col0 + C] if r >= 0 else state[slot, taps - 1 + r]
             acc = acc + weight[j] * x.float()
-        out[t] = _silu(acc).to(out.dtype)
+        out[t] = (_silu(acc) if activation else acc).to(out.dtype)
 
 
 def conv_state_update(state, u, col0, q_start, state_slot):
@@ -301,9 +305,10 @@ def ssm_scan(y, xbc, u, dt_col, dt_bias, a_log, d_skip, state, q_start, state_sl
             y[t] = (torch.einsum("hpn,hn->hp", state[slot], C) + d_skip[:, None] * x).reshape(-1)
 
 
-def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps, gate_after=False):
+def gated_group_rmsnorm(out, y, u, z_col, weight, parts, eps, gate_after=False, gate="silu"):
     n, inner = y.shape
-    gate = _silu(u[:, z_col : z_col + inner].float())
+    z = u[:, z_col : z_col + inner].float()
+    gate = torch.sigmoid(z) if gate == "sigmoid" else _silu(z)
     g = (y if gate_after else y * gate).view(n, parts, inner // parts)
     g = g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)
     out.copy_((g.view(n, inner) * weight * (gate if gate_after else 1.0)).to(out.dtype))
@@ -582,6 +587,166 @@ def diff_attention_tc(out, q, k_pool, v_pool, block_tables, q_start, kv_len, num
     diff_attention_simt(out, q, k_pool, v_pool, block_tables, seq, positions, gate, num_heads, scale, window, keep_first, lam, post, eps)
 
 
+# ---- a stream whose sublayer outputs carry a learned scale per feature; token shift; recurrences with a decay per channel; routed experts
+
+
+def add_rmsnorm_scaled(y, h, a, fa, b, fb, scale, weight, eps, rows=None):
+    delta = None
+    if a is not None:
+        delta = fa * a.float()
+        if b is not None:
+            delta = delta + fb * b.float()
+        delta = delta * scale
+    if rows is None:
+        if delta is not None:
+            h += delta
+        x = h
+    else:
+        x = h[rows.long()] + (delta[rows.long()] if delta is not None else 0.0)
+    if y is not None:
+        y.copy_((x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight).to(y.dtype))
+
+
+def concat_stream_rows(out, h, table, ids):
+    W = h.shape[1]
+    out[:, :W] = h.to(out.dtype)
+    out[:, W:] = table[ids.long()]
+
+
+def token_shift_blend(out, x, mu, state, seq_of_token, q_start, state_slot):
+    n = x.shape[0]
+    for t in range(n):
+        s = int(seq_of_token[t])
+        before = x[t - 1] if t > int(q_start[s]) else state[int(state_slot[s]), 0]
+        c = x[t].float()
+        out[:, t] = (c + (before.float() - c) * mu).to(out.dtype)
+
+
+def rotary_unit_store(q_out, x, positions, inv_freq, slots, k_pool, v_pool, num_heads, num_kv_heads, head_dim, value_dim, rotary_dim, unit_eps, page_size):
+    n = x.shape[0]
+    d, dv, D = head_dim, value_dim, max(head_dim, value_dim)
+    qk = x[:, : (num_heads + num_kv_heads) * d].float().reshape(n, num_heads + num_kv_heads, d).clone()
+    if rotary_dim:
+        half = rotary_dim // 2
+        ang = positions.float()[:, None] * inv_freq[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        lo, hi = qk[..., :half].clone(), qk[..., half:rotary_dim].clone()
+        qk[..., :half] = lo * cos - hi * sin
+        qk[..., half:rotary_dim] = hi * cos + lo * sin
+    if unit_eps is not None:
+        qk = qk * torch.rsqrt((qk * qk).mean(-1, keepdim=True) + unit_eps)
+    rows = torch.zeros((n, num_heads + num_kv_heads, D))
+    rows[..., :d] = qk
+    q_out.copy_(rows[:, :num_heads].reshape(n, num_heads * D).to(q_out.dtype))
+    if slots is not None:
+        page, off = (slots // page_size).long(), (slots % page_size).long()
+        k_pool[page, :, off, :] = rows[:, num_heads:].to(k_pool.dtype)
+        v = torch.zeros((n, num_kv_heads, D))
+        v[..., :dv] = x[:, (num_heads + num_kv_heads) * d :].float().reshape(n, num_kv_heads, dv)
+        v_pool[page, :, off, :] = v.to(v_pool.dtype)
+
+
+def _row_offsets(kq, heads, d, dv):
+    a, k, g = 0, kq * d, 2 * kq * d
+    v = g + heads * d
+    return a, k, g, v, v + heads * dv
+
+
+def shift_decay_prep(rows, rkvg, wz, w0, heads, d):
+    a, k, g, v, _ = _row_offsets(heads, heads, d, d)
+    I = heads * d
+    rows[:, a : a + I] = rkvg[0].float()
+    rows[:, k : k + I] = rkvg[1].float()
+    rows[:, v : v + I] = rkvg[2].float()
+    rows[:, g : g + I] = torch.exp(-torch.exp(wz.float() + w0))
+
+
+def channel_delta_prep(rows, qkv, u, b_col, a, dt_bias, a_log, heads, kv_heads, d, dv, unit_eps):
+    n = qkv.shape[0]
+    oa, ok, og, ov, ob = _row_offsets(kv_heads, heads, d, dv)
+    qk = kv_heads * d
+    q = qkv[:, :qk].float().view(n, kv_heads, d)
+    k = qkv[:, qk : 2 * qk].float().view(n, kv_heads, d)
+    rows[:, oa : oa + qk] = (q * torch.rsqrt((q * q).sum(-1, keepdim=True) + unit_eps) * d**-0.5).reshape(n, qk)
+    rows[:, ok : ok + qk] = (k * torch.rsqrt((k * k).sum(-1, keepdim=True) + unit_eps)).reshape(n, qk)
+    step = torch.nn.functional.softplus(a.float() + dt_bias, threshold=20.0).view(n, heads, d)
+    rows[:, og : og + heads * d] = torch.exp(-torch.exp(a_log)[None, :, None] * step).reshape(n, heads * d)
+    rows[:, ov : ov + heads * dv] = qkv[:, 2 * qk :].float()
+    rows[:, ob : ob + heads] = torch.sigmoid(u[:, b_col : b_col + heads].float())
+
+
+def decay_recurrence(o, rows, state, q_start, state_slot, kq_heads, mode, bonus=None, max_len=0):
+    _, heads, dv, d = state.shape  # the state is kept transposed: [slot, head, value column, key row]
+    oa, ok, og, ov, ob = _row_offsets(kq_heads, heads, d, dv)
+    fan = heads // kq_heads
+    for s in range(state_slot.numel()):
+        slot = int(state_slot[s])
+        for t in range(int(q_start[s]), int(q_start[s + 1])):
+            a = rows[t, oa : oa + kq_heads * d].view(kq_heads, d).repeat_interleave(fan, 0)
+            k = rows[t, ok : ok + kq_heads * d].view(kq_heads, d).repeat_interleave(fan, 0)
+            g = rows[t, og : og + heads * d].view(heads, d)
+            v = rows[t, ov : ov + heads * dv].view(heads, dv)
+            S = state[slot]
+            if mode == "bonus":
+                kv = v[:, :, None] * k[:, None, :]  # [heads, dv, d]
+                o[t] = torch.einsum("hvd,hd->hv", S + kv * bonus[:, None, :], a).reshape(-1)
+                state[slot] = S * g[:, None, :] + kv
+            else:
+                beta = rows[t, ob : ob + heads]
+                S = S * g[:, None, :]
+                w = beta[:, None] * (v - torch.einsum("hvd,hd->hv", S, k))
+                S = S + w[:, :, None] * k[:, None, :]
+                state[slot] = S
+                o[t] = torch.einsum("hvd,hd->hv", S, a).reshape(-1)
+
+
+def moe_route(ids, weights, x, router, correction, group_count, group_keep, scale):
+    n, top = ids.shape
+    E = router.shape[0]
+    s = torch.sigmoid(x.float() @ router.t())
+    choice = s + correction
+    if group_count > 1:
+        per = E // group_count
+        marks = choice.view(n, group_count, per).topk(min(2, per), -1).values.sum(-1)
+        order = torch.sort(-marks, dim=-1, stable=True).indices[:, :group_keep]
+        allowed = torch.zeros((n, group_count), dtype=torch.bool)
+        allowed.scatter_(1, order, True)
+        choice = torch.where(allowed.repeat_interleave(per, 1), choice, torch.full_like(choice, float("-inf")))
+    picked = torch.sort(-choice, dim=-1, stable=True).indices[:, :top]
+    w = s.gather(1, picked)
+    ids.copy_(picked.to(torch.int32))
+    weights.copy_(w / (w.sum(-1, keepdim=True) + 1e-20) * scale)
+
+
+def _glu_act(g, activation):
+    if activation == "gelu_tanh":
+        return _gelu_tanh(g)
+    if activation == "quick_gelu":
+        return g * torch.sigmoid(1.702 * g)
+    return _silu(g)
+
+
+def moe_experts(out, x, ids, weights, w_gate_up, w_down, activation="silu"):
+    n, top = ids.shape
+    ff = w_gate_up.shape[1] // 2
+    acc = torch.zeros((n, x.shape[1]))
+    for k in range(top):
+        for e in ids[:, k].unique().tolist():
+            rows = (ids[:, k] == e).nonzero().flatten()
+            gu = _sums(x[rows], w_gate_up[e]).to(x.dtype).float()
+            hidden = (_glu_act(gu[:, :ff], activation) * gu[:, ff:]).to(x.dtype)
+            acc[rows] += weights[rows, k, None] * _sums(hidden, w_down[e])
+    out.copy_(acc.to(out.dtype))
+
+
+def linear_bias(x, weight, bias):
+    return (_sums(x, weight) + bias.float()).to(x.dtype)
+
+
+def batched_project(x, weight):
+    return torch.bmm(x.float(), weight.float()).to(x.dtype)
+
+
 OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_page, "add_rmsnorm": add_rmsnorm,
        "rotary_table": rotary_table, "rotary_store": rotary_store, "silu_mul": silu_mul, "paged_attention_simt": paged_attention_simt,
        "paged_attention_mma": paged_attention_mma, "paged_decode_tma": paged_decode_tma, "paged_prefill_tc": paged_prefill_tc,
@@ -595,7 +760,9 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "heads_matvec": heads_matvec, "heads_matvec_supported": lambda in_features, features: True,
        "pair_embedding": pair_embedding, "group_norm_add": group_norm_add, "group_norm_rows": group_norm_rows, "gelu_mul_rows": gelu_mul_rows,
        "depth_average": depth_average, "mingru_scan": mingru_scan, "diff_prep": diff_prep, "diff_attention_simt": diff_attention_simt,
-       "diff_attention_tc": diff_attention_tc}
+       "diff_attention_tc": diff_attention_tc, "add_rmsnorm_scaled": add_rmsnorm_scaled, "concat_stream_rows": concat_stream_rows,
+       "token_shift_blend": token_shift_blend, "rotary_unit_store": rotary_unit_store, "shift_decay_prep": shift_decay_prep,
+       "channel_delta_prep": channel_delta_prep, "decay_recurrence": decay_recurrence, "moe_route": moe_route, "moe_experts": moe_experts}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered
@@ -616,6 +783,7 @@ def patched():
     saved = {name: getattr(ops, name) for name in OPS}
     saved_linear, saved_model_linear, saved_require = gemm.linear, model_mod.linear, runner_mod._require_cuda
     saved_logits, saved_need = gemm.logits_product, gemm._need_device
+    saved_bias, saved_batched = gemm.linear_bias, gemm.batched_project
     saved_lookup, saved_mixed = graphs_mod.DecodeGraphs.lookup, graphs_mod.DecodeGraphs.lookup_mixed
     try:
         graphs_mod.DecodeGraphs.lookup = graphs_mod.DecodeGraphs.lookup_mixed = lambda self, *a, **k: None  # no captured steps without a device
@@ -624,6 +792,7 @@ def patched():
             setattr(ops, name, _counted(name, fn))
         gemm.linear = model_mod.linear = linear
         gemm.logits_product, gemm._need_device = logits_product, lambda x, what: None
+        gemm.linear_bias, gemm.batched_project = linear_bias, batched_project
         runner_mod._require_cuda = lambda device: None
         yield
     finally:
@@ -631,5 +800,6 @@ def patched():
             setattr(ops, name, fn)
         gemm.linear, model_mod.linear, runner_mod._require_cuda = saved_linear, saved_model_linear, saved_require
         gemm.logits_product, gemm._need_device = saved_logits, saved_need
+        gemm.linear_bias, gemm.batched_project = saved_bias, saved_batched
         graphs_mod.DecodeGraphs.lookup, graphs_mod.DecodeGraphs.lookup_mixed = saved_lookup, saved_mixed
 
