@@ -590,7 +590,8 @@ def paged_attention_mma(
 
 
 def skinny_gemm_supported(tokens: int, in_features: int) -> bool:
-    return 1 <= tokens <= 256 and in_features >= 8 and in_features % 8 == 0
+    """Rows of at least one k-tile (64 numbers): the inner halves of low-rank products, shorter than that, stay with the library."""
+    return 1 <= tokens <= 256 and in_features >= 64 and in_features % 8 == 0
 
 
 class ScaledRows:

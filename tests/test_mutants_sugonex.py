@@ -37,7 +37,7 @@ MUTANTS = {
     "the attention ignores the window": (LatentAttention, "forward", "self.nh, self.scale, self.window, splits=", "self.nh, self.scale, None, splits="),
     "the latent space queries use the value matrix": (LatentAttention, "forward", "[:, :, : self.d], self.w_uk,", "[:, :, : self.d], self.w_uv.transpose(1, 2)[:, : self.d, :] if self.dv >= self.d else self.w_uk,"),
     "the output gate is left out": (LatentAttention, "forward", "if self.gated else None)", "if False else None)"),
-    "the rotated part does not rotate": (LatentAttention, "forward", "self.nh, self.d, self.dr, self.rank, self.rotary_dim, cache.page_size)", "self.nh, self.d, self.dr, self.rank, 0, cache.page_size)"),
+    "the rotated part does not rotate": (LatentAttention, "forward", "self.nh, self.d, self.dr, self.rank, self.rotary_dim, cache.page_size, amp=self.amp)", "self.nh, self.d, self.dr, self.rank, 0, cache.page_size, amp=self.amp)"),
     "beta and the decay change places": (GatedDeltaRule, "forward", "self.b_col, self.a_col, w[", "self.a_col, self.b_col, w["),
     "the convolution's carried inputs are not moved on": (GatedDeltaRule, "forward", "if self.taps > 1:", "if False:"),
     "the gate enters the norm": (GatedDeltaRule, "forward", "gate_after=True", "gate_after=False"),
