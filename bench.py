@@ -843,6 +843,150 @@ def pokadra_kernels(size, pk, tokens=4096, seqs=64):
     return out
 
 
+def lokolorn_sizes(width, heads, kv_heads, dim, rec_heads, rec_dim, delta_heads, delta_kv_heads, delta_dim, rot_dim, kv_rank, window, ff, experts, top, sg,
+                   vocab=32000):
+    """A Lokolorn model of eight layer runs (attention and token-shift recurrence side by side, delta rule with a decay per channel,
+    latent attention with a window and sinks, delta rule; the four run twice) whose routed feed-forward activates as many numbers a
+    token as a dense one of size ``ff`` (``top`` experts of ff / top), and the Sugonex configuration of the same width, heads,
+    feed-forward size and number of layer runs (``sg``: its sizes)."""
+    def mlp():
+        return {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+
+    par = {"type": "parallel", "mlp": mlp(), "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": 4, "scale": 1.0, "rot": {"base": 10000.0, "dims": dim}},
+        "right": {"heads": rec_heads, "dim": rec_dim, "decay_rank": 64}, "left_scale": 0.7, "right_scale": 0.7}}
+    dl = {"type": "channel_delta", "mlp": mlp(), "mixer": {"heads": delta_heads, "kv_heads": delta_kv_heads, "dim": delta_dim, "vdim": delta_dim, "conv": 4,
+                                                          "decay_rank": 64, "gate_rank": 64}}
+    lat = {"type": "latent_attention", "mlp": mlp(), "mixer": {
+        "heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5, "mask": {"size": window},
+        "rot": {"base": 500000.0, "dims": rot_dim, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    lk = {"architecture": "Lokolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": [par, dl, lat, dl],
+          "loop": {"start": 0, "stop": 4, "times": 2}}
+    sugonex, _ = sugonex_sizes(width=width, ff=ff, vocab=vocab, **sg)
+    return lk, sugonex
+
+
+LOKOLORN_SIZES = {
+    name: dict(width=s["width"], heads=s["heads"], kv_heads=s["pz"]["kv_heads"], dim=s["dim"], rec_heads=s["width"] // 64 // 2, rec_dim=64,
+               delta_heads=s["delta_heads"], delta_kv_heads=s["delta_kv_heads"], delta_dim=s["delta_dim"], rot_dim=s["rot_dim"], kv_rank=s["kv_rank"],
+               window=s["window"], ff=s["ff"], experts=16, top=4, sg={k: v for k, v in s.items() if k not in ("width", "ff")})
+    for name, s in SUGONEX_SIZES.items()
+}
+
+
+def lokolorn_kernels(size, pk, tokens=4096, seqs=64):
+    """Every kernel of the Lokolorn parts beside the like kernel of the Sugonex (or Llama) parts, at one size: a prompt portion of
+    ``tokens`` tokens and a decode step of ``seqs`` sequences.  us, the bytes (or operations) the kernel has to move, and the share of
+    the measured HBM peak (of the CUDA cores' float32 rate for the scans over a portion, of the measured bf16 rate for the products)."""
+    import torch
+
+    from dli_b200.kernels import gemm, ops
+
+    dev, bf = "cuda", torch.bfloat16
+    W, nh, nkv, d, ff = size["width"], size["heads"], size["kv_heads"], size["dim"], size["ff"]
+    Hr, dr_ = size["rec_heads"], size["rec_dim"]
+    Hd, Gd, dd = size["delta_heads"], size["delta_kv_heads"], size["delta_dim"]
+    E, top = size["experts"], size["top"]
+    eff = ff // top
+    out = {}
+
+    def record(name, us, nbytes, like=None, flops=None, tensor=False):
+        rec = {"us": round(us, 1), "gb_s": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops is not None and tensor:
+            rec["tflops_bf16"] = round(flops / us / 1e6, 1)
+            rec["bf16_frac"] = round(flops / us / 1e6 / pk["bf16_tflops"], 3)
+        elif flops is not None:
+            rec["tflops_fp32"] = round(flops / us / 1e6, 2)
+            rec["simt_frac"] = round(flops / us / 1e6 / SIMT_FP32_TFLOPS, 3)
+        if like:
+            rec["like"] = like
+        out[name] = rec
+
+    for label, n, S in (("portion", tokens, 1), ("decode", seqs, seqs)):
+        q_len = n // S
+        q_start = torch.arange(S + 1, dtype=torch.int32, device=dev) * q_len
+        seq_of = torch.repeat_interleave(torch.arange(S, dtype=torch.int32), q_len).to(dev)
+        slot = torch.arange(S, dtype=torch.int32, device=dev)
+        positions = (torch.arange(n, dtype=torch.int32) % q_len + (0 if S == 1 else 2048)).to(dev)
+        # the norm that adds a scaled sublayer output (two terms, as behind a parallel mixer), beside the norm with two deltas
+        h = torch.randn(n, W, device=dev)
+        a, b = torch.randn(n, W, device=dev).to(bf), torch.randn(n, W, device=dev).to(bf)
+        w1 = torch.ones(W, device=dev)
+        y1, y2 = torch.empty(n, W, dtype=bf, device=dev), torch.empty(n, W, dtype=bf, device=dev)
+        record(f"{label}.add_rmsnorm_scaled", time_kernel(lambda: ops.add_rmsnorm_scaled(y1, h, a, 0.7, b, 0.7, w1, w1, 1e-6)), n * W * 14, "add_rmsnorm_pair")
+        record(f"{label}.add_rmsnorm_pair", time_kernel(lambda: ops.add_rmsnorm_pair(y1, y2, h, a, b, w1, w1, 1e-6)), n * W * 16)
+        # loop entry and token shift
+        table, ids = torch.randn(32000, W, device=dev).to(bf), torch.randint(0, 32000, (n,), dtype=torch.int32, device=dev)
+        both = torch.empty(n, 2 * W, dtype=bf, device=dev)
+        record(f"{label}.concat_stream_rows", time_kernel(lambda: ops.concat_stream_rows(both, h, table, ids)), n * W * 10)
+        x = torch.randn(n, W, device=dev).to(bf)
+        mu, shift = torch.rand(5, W, device=dev), torch.zeros(S, 1, W, dtype=bf, device=dev)
+        blends = torch.empty(5, n, W, dtype=bf, device=dev)
+        record(f"{label}.token_shift_blend", time_kernel(lambda: ops.token_shift_blend(blends, x, mu, shift, seq_of, q_start, slot)), n * W * 12)
+        # attention half: convolution without activation, then rotation + unit RMS + pages
+        C = (nh + 2 * nkv) * d
+        u = torch.randn(n, C, device=dev).to(bf)
+        mixed = torch.empty(n, C, dtype=bf, device=dev)
+        cw, cstate = torch.randn(4, C, device=dev), torch.zeros(S, 3, C, dtype=bf, device=dev)
+        record(f"{label}.causal_conv", time_kernel(lambda: ops.causal_conv_silu(mixed, u, 0, cw, None, cstate, seq_of, q_start, slot, activation=False)), n * C * 4,
+               "causal_conv_silu")
+        pages = n // 16 + S + 1
+        kp, vp = (torch.zeros(pages, nkv, 16, d, dtype=bf, device=dev) for _ in range(2))
+        slots = torch.arange(n, dtype=torch.int32, device=dev)
+        inv = (1.0 / (10000.0 ** (torch.arange(0, d, 2).float() / d))).to(dev)
+        q = torch.empty(n, nh * d, dtype=bf, device=dev)
+        record(f"{label}.rotary_unit_store", time_kernel(lambda: ops.rotary_unit_store(q, mixed, positions, inv, slots, kp, vp, nh, nkv, d, d, d, 1e-6, 16)),
+               n * C * 4, "qk_norm_rotary_store")
+        proj = torch.randn(n, (nh + 2 * nkv) * d, device=dev).to(bf)
+        wq, wk = torch.ones(nh * d, device=dev), torch.ones(nkv * d, device=dev)
+        record(f"{label}.qk_norm_rotary_store", time_kernel(lambda: ops.qk_norm_rotary_store(proj, wq, wk, 1e-6, positions, inv, slots, kp, vp, nh, nkv, d, d, 16,
+                                                                                             True, False)), n * C * 4)
+        # the two recurrences: float32 rows, then the walk; their like: the delta rule with one decay per head
+        Ir = Hr * dr_
+        rkvg, wz, w0 = torch.randn(4, n, Ir, device=dev).to(bf), torch.randn(n, Ir, device=dev).to(bf), torch.full((Ir,), -3.0, device=dev)
+        rows = torch.empty(n, ops.decay_recurrence_row(Hr, Hr, dr_, dr_), device=dev)
+        record(f"{label}.shift_decay_prep", time_kernel(lambda: ops.shift_decay_prep(rows, rkvg, wz, w0, Hr, dr_)), n * Ir * (8 + 16))
+        st = torch.zeros(S, Hr, dr_, dr_, device=dev)
+        o = torch.empty(n, Ir, device=dev)
+        bonus = torch.randn(Hr, dr_, device=dev)
+        us = time_kernel(lambda: ops.decay_recurrence(o, rows, st, q_start, slot, Hr, "bonus", bonus, max_len=q_len))
+        record(f"{label}.recurrence_bonus", us, S * Hr * dr_ * dr_ * 8 + n * Ir * 20, "delta_rule_scan", flops=6.0 * n * Hr * dr_ * dr_)
+        qk, inner = Gd * dd, Hd * dd
+        qkv = torch.randn(n, 2 * qk + inner, device=dev).to(bf)
+        uu = torch.randn(n, 2 * qk + inner + Hd + 128, device=dev).to(bf)
+        aa, dtb, al = torch.randn(n, Hd * dd, device=dev).to(bf), torch.zeros(Hd * dd, device=dev), torch.full((Hd,), -3.0, device=dev)
+        rows2 = torch.empty(n, ops.decay_recurrence_row(Gd, Hd, dd, dd), device=dev)
+        record(f"{label}.channel_delta_prep", time_kernel(lambda: ops.channel_delta_prep(rows2, qkv, uu, 2 * qk + inner, aa, dtb, al, Hd, Gd, dd, dd, 1e-6)),
+               n * (2 * qk + 2 * inner) * 6)
+        st2 = torch.zeros(S, Hd, dd, dd, device=dev)
+        o2 = torch.empty(n, inner, device=dev)
+        us = time_kernel(lambda: ops.decay_recurrence(o2, rows2, st2, q_start, slot, Gd, "delta", None, max_len=q_len))
+        record(f"{label}.recurrence_delta", us, S * Hd * dd * dd * 8 + n * (2 * qk + 2 * inner) * 4 + n * inner * 4, "delta_rule_scan", flops=8.0 * n * Hd * dd * dd)
+        u3 = torch.randn(n, 2 * qk + 2 * inner + 2 * Hd, device=dev).to(bf)
+        dt1, al1 = torch.zeros(Hd, device=dev), torch.full((Hd,), -3.0, device=dev)
+        us = time_kernel(lambda: ops.delta_rule_scan(o2, qkv, u3, 2 * qk + 2 * inner, 2 * qk + 2 * inner + Hd, dt1, al1, st2, seq_of, q_start, slot, Gd, dd, 1e-6, max_len=q_len))
+        record(f"{label}.delta_rule_scan", us, S * Hd * dd * dd * 8 + n * ((2 * qk + inner) * 2 + inner * 4), flops=8.0 * n * Hd * dd * dd)
+        # routed feed-forward: router, experts; its like: the dense gated feed-forward of the same active size (library products + SiLU * up)
+        router, corr = torch.randn(E, W, device=dev) * 0.05, torch.randn(E, device=dev) * 0.1
+        ids2, wts = torch.empty(n, top, dtype=torch.int32, device=dev), torch.empty(n, top, device=dev)
+        record(f"{label}.moe_route", time_kernel(lambda: ops.moe_route(ids2, wts, x, router, corr, 4, 2, 2.5)), n * W * 2 + E * W * 4)
+        wgu, wd = (torch.randn(E, 2 * eff, W, device=dev) * 0.02).to(bf), (torch.randn(E, W, eff, device=dev) * 0.02).to(bf)
+        y = torch.empty(n, W, dtype=bf, device=dev)
+        flops = 6.0 * n * top * eff * W
+        hit = min(E, n * top)
+        record(f"{label}.moe_experts", time_kernel(lambda: ops.moe_experts(y, x, ids2, wts, wgu, wd, "silu")), hit * 3 * eff * W * 2 + n * W * 4, "dense_glu", flops=flops,
+               tensor=True)
+        dgu, ddn = (torch.randn(2 * ff, W, device=dev) * 0.02).to(bf), (torch.randn(W, ff, device=dev) * 0.02).to(bf)
+        act = torch.empty(n, ff, dtype=bf, device=dev)
+
+        def dense():
+            ops.silu_mul(act, gemm.project(x, dgu), False)
+            return gemm.project(act, ddn)
+
+        record(f"{label}.dense_glu", time_kernel(dense), 3 * ff * W * 2 + n * W * 4, flops=6.0 * n * ff * W, tensor=True)
+    return out
+
+
 SIMT_FP32_TFLOPS = 148 * 128 * 2 * 1.9e9 / 1e12  # CUDA-core multiply-adds of a B200 at 1.9 GHz: the scan's ceiling (no float32 tensor-core path)
 
 
@@ -851,6 +995,7 @@ DESIGNS = {
     "pazenex": (DESIGN_SIZES, pazenex_sizes, "llama", design_kernels),
     "sugonex": (SUGONEX_SIZES, sugonex_sizes, "pazenex", sugonex_kernels),
     "pokadra": (POKADRA_SIZES, pokadra_sizes, "pazenex", pokadra_kernels),
+    "lokolorn": (LOKOLORN_SIZES, lokolorn_sizes, "sugonex", lokolorn_kernels),
 }
 
 
@@ -1092,7 +1237,7 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "sample"],
                     help="profiling runs: only the device-timed decode steps, only the prefill step, or only the sampling kernel (prints a short line)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling runs: launch the step's kernels one by one")
-    ap.add_argument("--design", default=None, choices=["pazenex", "sugonex", "pokadra"],
+    ap.add_argument("--design", default=None, choices=["pazenex", "sugonex", "pokadra", "lokolorn"],
                     help="another measurement: this architecture beside Llama at equal sizes, and its kernels beside their likes (prints its own line)")
     ap.add_argument("--size", default=None, choices=list(DESIGN_SIZES), help="--design: one size only (every design has these names)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,

@@ -1564,6 +1564,14 @@ def decay_recurrence(o: torch.Tensor, rows: torch.Tensor, state: torch.Tensor, q
 # ------------------------------------------------------------------ routed mixture of gated feed-forwards
 
 MOE_MAX_TOP = 32
+MOE_GROUPED_TILE_ROWS = 64  # BM of csrc/moe_grouped.cu
+MOE_GROUPED_MIN_TOKENS = 17  # up to 16 tokens a step reads every chosen expert once per pair, on the CUDA cores
+
+
+def moe_grouped_supported(tokens: int, W: int, ff: int, dtype: torch.dtype) -> bool:
+    """Whether the experts' products of a step go to the grouped tensor-core kernels: bfloat16, more tokens than a decode step
+    brings, rows of whole 16-byte chunks."""
+    return dtype == torch.bfloat16 and tokens >= MOE_GROUPED_MIN_TOKENS and W % 8 == 0 and ff % 8 == 0
 MOE_PAIR_CHUNK = 8192  # tokens a launch of the pair kernels takes (their grids count (token, expert) pairs along y)
 
 
@@ -1599,10 +1607,22 @@ def moe_experts(out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: 
     if (out.dtype not in DT_CODE or tuple(out.shape) != (n, W) or w_gate_up.shape[2] != W or tuple(w_down.shape) != (E, W, ff) or tuple(ids.shape) != (n, top)
             or tuple(weights.shape) != (n, top) or activation not in GLU_ACTIVATIONS):
         raise KernelError("moe_experts: shapes, dtype or activation do not agree")
+    global launch_count
+    if moe_grouped_supported(n, W, ff, out.dtype):
+        # many tokens: the pairs sorted by expert, two grouped products on the tensor cores (csrc/moe_grouped.cu)
+        tiles = (min(n * top, E) + n * top // MOE_GROUPED_TILE_ROWS)
+        rows = tiles * MOE_GROUPED_TILE_ROWS
+        ints = torch.empty(2 * (E + 1) + 2 * n * top + tiles + rows, dtype=torch.int32, device=out.device)
+        hidden = torch.empty((rows, ff), dtype=out.dtype, device=out.device)
+        partial = torch.empty((rows, W), dtype=torch.float32, device=out.device)
+        g = _fn("moe_grouped.cu", "dli_moe_grouped", [c_void_p] * 9 + [c_int] * 6 + [c_void_p])
+        _check(g(_ptr(out), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), _ptr(ints), _ptr(hidden), _ptr(partial), n, W, ff, E, top,
+                 GLU_ACTIVATIONS[activation], _stream()), "moe_experts")
+        launch_count += 6  # seven kernels a call
+        return
     f = _fn("moe.cu", "dli_moe_pairs", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
     step = max(1, min(MOE_PAIR_CHUNK, 65535 // top))
     hidden = torch.empty((min(n, step) * top, ff), dtype=out.dtype, device=out.device)
-    global launch_count
     for t0 in range(0, n, step):
         m = min(step, n - t0)
         _check(f(_ptr(out[t0:]), _ptr(hidden), _ptr(x[t0:]), _ptr(ids[t0:]), _ptr(weights[t0:]), _ptr(w_gate_up), _ptr(w_down), m, W, ff, top,

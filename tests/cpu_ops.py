@@ -762,7 +762,7 @@ OPS = {"embedding": embedding, "patch_tokens": patch_tokens, "copy_page": copy_p
        "depth_average": depth_average, "mingru_scan": mingru_scan, "diff_prep": diff_prep, "diff_attention_simt": diff_attention_simt,
        "diff_attention_tc": diff_attention_tc, "add_rmsnorm_scaled": add_rmsnorm_scaled, "concat_stream_rows": concat_stream_rows,
        "token_shift_blend": token_shift_blend, "rotary_unit_store": rotary_unit_store, "shift_decay_prep": shift_decay_prep,
-       "channel_delta_prep": channel_delta_prep, "decay_recurrence": decay_recurrence, "moe_route": moe_route, "moe_experts": moe_experts}
+       "moe_grouped_supported": lambda tokens, W, ff, dtype: False, "channel_delta_prep": channel_delta_prep, "decay_recurrence": decay_recurrence, "moe_route": moe_route, "moe_experts": moe_experts}
 
 
 calls: dict[str, int] = {}  # how often each stand-in ran since patched() was entered

@@ -20,7 +20,7 @@ def test_case(case, dtype, tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_replay_with_four_state_slots(dtype, tmp_path):
     """bin/trace_run on a schedule of six requests, four live at most, in a pool that holds three of them."""
-    cfg = suite.CONFIGS["mixed_loop"]
+    cfg = suite.pick("mixed_loop", dtype)
     w = suite.make_model(tmp_path / "m", cfg, seed=41)
     seqs = {f"r{i}": suite.tokens_for(cfg, n, seed=80 + i) for i, n in enumerate((40, 33, 21, 38, 27, 30))}
     want = {r: plain.forward(cfg, w, t) for r, t in seqs.items()}
@@ -57,7 +57,7 @@ def test_steps_replayed_from_graphs(dtype, tmp_path):
     """Steps of single tokens replay a CUDA graph; a step shape that keeps coming (a short portion of one request beside single
     tokens of two others) is captured after 32 sightings.  Padding rows use the scratch page and the scratch state slot.  Logits
     before and after the capture equal the plain model's."""
-    cfg = suite.CONFIGS["mixed_loop"]
+    cfg = suite.pick("mixed_loop", dtype)
     w = suite.make_model(tmp_path / "m", cfg, seed=43)
     s = suite.Session(tmp_path / "m", "cuda:0", dtype, pages=120, page_size=8)
     assert s.runner.graphs is not None
