@@ -174,7 +174,7 @@ def _parse_mlp(m: dict, where: str) -> RoutedMlpConfig:
     return RoutedMlpConfig(_positive(m["expert"]["ff"], where + ".expert.ff"), experts, top, float(r["scale"]), count, keep)
 
 
-_MIXERS = {"parallel": _parse_parallel, "channel_delta": _parse_channel_delta, "latent_attention": _parse_latent}
+_MIXERS = {"parallel": "_parse_parallel", "channel_delta": "_parse_channel_delta", "latent_attention": "_parse_latent"}  # looked up by name at every call
 
 
 @dataclass(frozen=True)
@@ -197,7 +197,7 @@ class LokolornConfig:
             _keys(entry, where, ("type", "mixer"), ("mlp",))
             if entry["type"] not in _MIXERS:
                 raise UnsupportedModelError(f"{where}.type={entry['type']!r} (known: {', '.join(_MIXERS)})")
-            mixer = _MIXERS[entry["type"]](entry["mixer"], where + ".mixer")
+            mixer = globals()[_MIXERS[entry["type"]]](entry["mixer"], where + ".mixer")
             layers.append(LokolornLayerConfig(mixer, None if entry.get("mlp") is None else _parse_mlp(entry["mlp"], where + ".mlp")))
         loop = None
         if cfg.get("loop") is not None:

@@ -84,8 +84,8 @@ __global__ void channel_delta_prep_kernel(float* __restrict__ rows, const T* __r
 }
 
 constexpr int REC_R = 32;       // key rows of a state column that one thread keeps in registers
-constexpr int REC_THREADS = 128;
-constexpr int REC_TOKENS = 8;   // tokens staged in shared memory at a time
+constexpr int REC_THREADS = 128;  // at most; a CTA has as many threads as its columns need
+constexpr int REC_TOKENS = 16;  // tokens staged in shared memory at a time, the next sixteen on their way meanwhile
 
 // Staged vectors are laid out in slices of REC_R floats, each followed by 4 floats of padding, so that the threads of a
 // warp that hold different slices read different banks.
@@ -93,11 +93,21 @@ __host__ __device__ inline int slice_at(int i) { return i + ((i / REC_R) << 2); 
 __host__ __device__ inline int staged_floats(int ks) { return ks * (REC_R + 4); }
 __host__ __device__ inline int token_floats(int ks, int cols) { return (3 * staged_floats(ks) + cols + 1 + 3) & ~3; }
 
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // One CTA: some value columns of one head of one sequence.  KS threads (consecutive lanes) share a column, each with
 // REC_R key rows of it in registers (rows beyond d are zeros).  MODE 0 (bonus): o = sum_i a_i (S_i + u_i k_i v);
 // S_i <- g_i S_i + k_i v.  MODE 1 (delta): S_i <- g_i S_i; w = beta (v - sum_i k_i S_i); S_i <- S_i + k_i w; o = sum_i a_i S_i.
 // state [slots][heads][dv][d] (a value column's key rows are contiguous).  Sums over the key rows are added in an
 // order fixed by d alone, token after token, so a result does not depend on how a sequence was cut into steps.
+// Tokens arrive by asynchronous copies, sixteen at a time, the next sixteen under way while these are walked.
 template <int MODE>
 __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __restrict__ o, const float* __restrict__ rows,
                                                                        float* __restrict__ state, const int* __restrict__ q_start,
@@ -111,50 +121,91 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
   if (t1 <= t0) return;
   const RowLayout L = row_layout(kq, heads, d, dv);
   const int kqh = head / (heads / kq);
-  const int dfull = ks * REC_R, dpad = staged_floats(ks);
+  const int dpad = staged_floats(ks);
   const int tok_floats = token_floats(ks, cols_per_cta);  // per staged token: A | K | G | V of this CTA's columns | beta
-  const int tid = threadIdx.x;
+  const int buf_floats = REC_TOKENS * tok_floats;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
   const int col_local = tid / ks, slice = tid - col_local * ks;
   const int col0 = blockIdx.x * cols_per_cta;
   const int col = col0 + col_local;
   const bool active = col_local < cols_per_cta && col < dv;
   const int i0 = slice * REC_R;
+  const bool vec = (d & 3) == 0;  // rows of whole 16-byte chunks (the row's parts then start on 16-byte boundaries too)
+
+  // the places behind the head size stay zero in both buffers: no copy writes them
+  for (int e = tid; e < 2 * buf_floats; e += nthreads) sm[e] = 0.f;
+  __syncthreads();
+
+  auto stage = [&](int buf, int base) {
+    const int cnt = min(REC_TOKENS, t1 - base);
+    float* dst0 = sm + buf * buf_floats;
+    if (vec) {
+      const int chunks = d >> 2;
+      for (int e = tid; e < cnt * 3 * chunks; e += nthreads) {
+        const int tok = e / (3 * chunks), rem = e - tok * 3 * chunks;
+        const int which = rem / chunks, i = (rem - which * chunks) << 2;
+        const float* row = rows + (size_t)(base + tok) * L.stride;
+        const float* src = which == 0 ? row + L.a + kqh * d + i : (which == 1 ? row + L.k + kqh * d + i : row + L.g + head * d + i);
+        copy_async16(dst0 + tok * tok_floats + which * dpad + slice_at(i), src);
+      }
+    } else {
+      for (int e = tid; e < cnt * 3 * d; e += nthreads) {
+        const int tok = e / (3 * d), rem = e - tok * 3 * d;
+        const int which = rem / d, i = rem - which * d;
+        const float* row = rows + (size_t)(base + tok) * L.stride;
+        const float* src = which == 0 ? row + L.a + kqh * d + i : (which == 1 ? row + L.k + kqh * d + i : row + L.g + head * d + i);
+        copy_async4(dst0 + tok * tok_floats + which * dpad + slice_at(i), src);
+      }
+    }
+    const int extra = cols_per_cta + (MODE == 1 ? 1 : 0);
+    for (int e = tid; e < cnt * extra; e += nthreads) {
+      const int tok = e / extra, c = e - tok * extra;
+      const float* row = rows + (size_t)(base + tok) * L.stride;
+      if (c == cols_per_cta) copy_async4(dst0 + tok * tok_floats + 3 * dpad + c, row + L.b + head);
+      else if (col0 + c < dv) copy_async4(dst0 + tok * tok_floats + 3 * dpad + c, row + L.v + head * dv + col0 + c);
+    }
+  };
+
+  stage(0, t0);
+  copy_commit();
 
   float S[REC_R], U[REC_R];
   float* srow = state + (((size_t)state_slot[seq] * heads + head) * dv + (active ? col : 0)) * d;
+  if (vec) {
 #pragma unroll
-  for (int r = 0; r < REC_R; ++r) {
-    const int i = i0 + r;
-    S[r] = (active && i < d) ? srow[i] : 0.f;
-    U[r] = (MODE == 0 && i < d) ? bonus[(size_t)head * d + i] : 0.f;
+    for (int r = 0; r < REC_R; r += 4) {
+      const int i = i0 + r;
+      float4 sv = make_float4(0.f, 0.f, 0.f, 0.f), uv = sv;
+      if (i < d) {
+        if (active) sv = *reinterpret_cast<const float4*>(srow + i);
+        if (MODE == 0) uv = *reinterpret_cast<const float4*>(bonus + (size_t)head * d + i);
+      }
+      S[r] = sv.x; S[r + 1] = sv.y; S[r + 2] = sv.z; S[r + 3] = sv.w;
+      U[r] = uv.x; U[r + 1] = uv.y; U[r + 2] = uv.z; U[r + 3] = uv.w;
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < REC_R; ++r) {
+      const int i = i0 + r;
+      S[r] = (active && i < d) ? srow[i] : 0.f;
+      U[r] = (MODE == 0 && i < d) ? bonus[(size_t)head * d + i] : 0.f;
+    }
   }
 
-  for (int base = t0; base < t1; base += REC_TOKENS) {
+  int buf = 0;
+  for (int base = t0; base < t1; base += REC_TOKENS, buf ^= 1) {
     const int cnt = min(REC_TOKENS, t1 - base);
-    __syncthreads();  // the tile before has been read
-    for (int e = tid; e < cnt * 3 * dfull; e += REC_THREADS) {
-      const int tok = e / (3 * dfull), rem = e - tok * 3 * dfull;
-      const int which = rem / dfull, i = rem - which * dfull;
-      const float* row = rows + (size_t)(base + tok) * L.stride;
-      float v = 0.f;
-      if (i < d) v = which == 0 ? row[L.a + kqh * d + i] : (which == 1 ? row[L.k + kqh * d + i] : row[L.g + head * d + i]);
-      sm[tok * tok_floats + which * dpad + slice_at(i)] = v;
-    }
-    for (int e = tid; e < cnt * (cols_per_cta + 1); e += REC_THREADS) {
-      const int tok = e / (cols_per_cta + 1), c = e - tok * (cols_per_cta + 1);
-      const float* row = rows + (size_t)(base + tok) * L.stride;
-      float v = 0.f;
-      if (c == cols_per_cta) v = MODE == 1 ? row[L.b + head] : 0.f;
-      else if (col0 + c < dv) v = row[L.v + head * dv + col0 + c];
-      sm[tok * tok_floats + 3 * dpad + c] = v;
-    }
+    if (base + REC_TOKENS < t1) stage(buf ^ 1, base + REC_TOKENS);  // (its readers finished before the barrier that ended the last round)
+    copy_commit();
+    copy_wait<1>();
     __syncthreads();
+    const float* tile = sm + buf * buf_floats;
     for (int tok = 0; tok < cnt; ++tok) {
-      const float4* A = reinterpret_cast<const float4*>(sm + tok * tok_floats + slice_at(i0));
-      const float4* K = reinterpret_cast<const float4*>(sm + tok * tok_floats + dpad + slice_at(i0));
-      const float4* G = reinterpret_cast<const float4*>(sm + tok * tok_floats + 2 * dpad + slice_at(i0));
-      const float v = sm[tok * tok_floats + 3 * dpad + (col_local < cols_per_cta ? col_local : 0)];
-      float acc = 0.f;
+      const float4* A = reinterpret_cast<const float4*>(tile + tok * tok_floats + slice_at(i0));
+      const float4* K = reinterpret_cast<const float4*>(tile + tok * tok_floats + dpad + slice_at(i0));
+      const float4* G = reinterpret_cast<const float4*>(tile + tok * tok_floats + 2 * dpad + slice_at(i0));
+      const float v = tile[tok * tok_floats + 3 * dpad + (col_local < cols_per_cta ? col_local : 0)];
+      float acc4[4] = {0.f, 0.f, 0.f, 0.f};  // four running sums: the chain of dependent multiply-adds is a quarter as long
       if (MODE == 0) {
 #pragma unroll
         for (int r = 0; r < REC_R; r += 4) {
@@ -163,13 +214,13 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const float kv = kvv[q] * v;
-            acc = fmaf(av[q], fmaf(U[r + q], kv, S[r + q]), acc);
+            acc4[q] = fmaf(av[q], fmaf(U[r + q], kv, S[r + q]), acc4[q]);
             S[r + q] = fmaf(gv[q], S[r + q], kv);
           }
         }
       } else {
-        const float beta = sm[tok * tok_floats + 3 * dpad + cols_per_cta];
-        float ks_sum = 0.f;
+        const float beta = tile[tok * tok_floats + 3 * dpad + cols_per_cta];
+        float ks4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < REC_R; r += 4) {
           const float4 k = K[r >> 2], g = G[r >> 2];
@@ -177,9 +228,10 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             S[r + q] *= gv[q];
-            ks_sum = fmaf(kvv[q], S[r + q], ks_sum);
+            ks4[q] = fmaf(kvv[q], S[r + q], ks4[q]);
           }
         }
+        float ks_sum = (ks4[0] + ks4[1]) + (ks4[2] + ks4[3]);
         for (int off = 1; off < ks; off <<= 1) ks_sum += __shfl_xor_sync(0xffffffffu, ks_sum, off);
         const float w = beta * (v - ks_sum);
 #pragma unroll
@@ -189,19 +241,30 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             S[r + q] = fmaf(kvv[q], w, S[r + q]);
-            acc = fmaf(av[q], S[r + q], acc);
+            acc4[q] = fmaf(av[q], S[r + q], acc4[q]);
           }
         }
       }
+      float acc = (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);
       for (int off = 1; off < ks; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
       if (active && slice == 0) o[(size_t)(base + tok) * heads * dv + (size_t)head * dv + col] = acc;
     }
+    __syncthreads();  // this buffer is copied into again in the round after next
   }
+  copy_wait<0>();
   if (active) {
+    if (vec) {
 #pragma unroll
-    for (int r = 0; r < REC_R; ++r) {
-      const int i = i0 + r;
-      if (i < d) srow[i] = S[r];
+      for (int r = 0; r < REC_R; r += 4) {
+        const int i = i0 + r;
+        if (i < d) *reinterpret_cast<float4*>(srow + i) = make_float4(S[r], S[r + 1], S[r + 2], S[r + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < REC_R; ++r) {
+        const int i = i0 + r;
+        if (i < d) srow[i] = S[r];
+      }
     }
   }
 }
@@ -249,9 +312,12 @@ DLI_EXPORT int dli_decay_recurrence(float* o, const float* rows, float* state, c
     return DLI_ERR_UNSUPPORTED;
   int ks = 1;
   while (ks * REC_R < d) ks <<= 1;
+  // columns a CTA: all that 128 threads hold, fewer while the grid would leave SMs idle (never under a warp's worth of threads)
   int cols = REC_THREADS / ks;
   if (cols > dv) cols = dv;
-  const size_t smem = (size_t)REC_TOKENS * token_floats(ks, cols) * sizeof(float);
+  while (cols * ks > 32 && (long long)((dv + cols - 1) / cols) * heads * num_seqs < 2LL * sm_count()) cols = (cols + 1) / 2;
+  int threads = ((cols * ks + 31) / 32) * 32;
+  const size_t smem = (size_t)2 * REC_TOKENS * token_floats(ks, cols) * sizeof(float);
   const dim3 grid((dv + cols - 1) / cols, heads, num_seqs);
   cudaError_t e;
   if (mode == 0) {
@@ -261,7 +327,7 @@ DLI_EXPORT int dli_decay_recurrence(float* o, const float* rows, float* state, c
       if (e != cudaSuccess) return (int)e;
       set.here() = (int)smem;
     }
-    e = launch_pdl((decay_recurrence_kernel<0>), grid, dim3(REC_THREADS), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, kq, d,
+    e = launch_pdl((decay_recurrence_kernel<0>), grid, dim3(threads), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, kq, d,
                    dv, ks, cols);
   } else {
     static MaxPerDevice set;
@@ -270,7 +336,7 @@ DLI_EXPORT int dli_decay_recurrence(float* o, const float* rows, float* state, c
       if (e != cudaSuccess) return (int)e;
       set.here() = (int)smem;
     }
-    e = launch_pdl((decay_recurrence_kernel<1>), grid, dim3(REC_THREADS), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, kq, d,
+    e = launch_pdl((decay_recurrence_kernel<1>), grid, dim3(threads), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, kq, d,
                    dv, ks, cols);
   }
   return (int)e;

@@ -29,7 +29,9 @@ SKINNY_MAX_TOKENS_HEAD = 64
 
 def decode_product(x: torch.Tensor, max_tokens: int = SKINNY_MAX_TOKENS) -> bool:
     """Whether a product with these activations goes to the engine's own decode kernel."""
-    return x.dtype == torch.bfloat16 and x.shape[0] <= max_tokens and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
+    # (TMA reads the activations: a column slice of one row is "contiguous" and yet may start off a 16-byte boundary)
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= max_tokens and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
+            and x.is_contiguous() and x.data_ptr() % 16 == 0)
 
 
 # Up to this many tokens the decode product also finishes the next elementwise step (rotary and

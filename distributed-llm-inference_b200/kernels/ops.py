@@ -590,8 +590,7 @@ def paged_attention_mma(
 
 
 def skinny_gemm_supported(tokens: int, in_features: int) -> bool:
-    """Rows of at least one k-tile (64 numbers): the inner halves of low-rank products, shorter than that, stay with the library."""
-    return 1 <= tokens <= 256 and in_features >= 64 and in_features % 8 == 0
+    return 1 <= tokens <= 256 and in_features >= 8 and in_features % 8 == 0
 
 
 class ScaledRows:
@@ -1565,7 +1564,7 @@ def decay_recurrence(o: torch.Tensor, rows: torch.Tensor, state: torch.Tensor, q
 
 MOE_MAX_TOP = 32
 MOE_GROUPED_TILE_ROWS = 64  # BM of csrc/moe_grouped.cu
-MOE_GROUPED_MIN_TOKENS = 17  # up to 16 tokens a step reads every chosen expert once per pair, on the CUDA cores
+MOE_GROUPED_MIN_TOKENS = 4  # fewer tokens rarely share an expert: every chosen expert is read once per pair, on the CUDA cores
 
 
 def moe_grouped_supported(tokens: int, W: int, ff: int, dtype: torch.dtype) -> bool:

@@ -306,7 +306,7 @@ class ChannelDeltaRule(Part):
     """The delta rule with one decay per head and KEY CHANNEL, on any mix of prompt portions and decoded tokens; the state
     is a matrix S (head_dim x value_dim) per head.
 
-    One product yields q | k | v | b | a1 | g1 (q and k: ``num_kv_heads`` heads of ``head_dim``; v: ``num_heads`` heads of
+    One product yields q | k | v | a1 | g1 | b (q and k: ``num_kv_heads`` heads of ``head_dim``; v: ``num_heads`` heads of
     ``value_dim``; b: one number per head; a1 and g1: the inner halves of two low-rank products).  q | k | v pass a causal
     convolution per channel (``conv_taps`` taps, no bias) and SiLU; q and k are then made unit vectors per head (float32;
     ``unit_eps`` inside the root) and q is multiplied by head_dim^-1/2.  Head h reads q/k head h // (num_heads / num_kv_heads).
@@ -337,7 +337,7 @@ class ChannelDeltaRule(Part):
             raise ValueError(f"channel_delta: head_dim={self.d} is above the scan kernel's {ops.RECURRENCE_MAX_HEAD_DIM}")
         self.qk, self.inner = self.kv_heads * self.d, self.heads * self.dv
         self.channels = 2 * self.qk + self.inner  # what passes the convolution: q | k | v
-        self.b_col = self.channels
+        self.b_col = self.channels  # set at load, behind the low-rank products' inner halves
         defaults = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "b": "b_proj.weight", "a1": "a1.weight", "a2": "a2.weight",
                     "g1": "g1.weight", "g2": "g2.weight", "o": "o_proj.weight", "A_log": "A_log", "dt_bias": "dt_bias", "norm": "norm.weight",
                     "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
@@ -361,11 +361,11 @@ class ChannelDeltaRule(Part):
 
     def load(self, tensors):
         t = {role: tensors[name] for role, name in self.names.items()}
-        a0 = self.b_col + self.heads
-        self.a_cols = (a0, a0 + t["a1"].shape[0])
+        self.a_cols = (self.channels, self.channels + t["a1"].shape[0])
         self.g_cols = (self.a_cols[1], self.a_cols[1] + t["g1"].shape[0])
+        self.b_col = self.g_cols[1]  # the betas' columns come last: the low-rank products' inner halves start on even columns
         self.w = {
-            "in": torch.cat([t["q"], t["k"], t["v"], t["b"], t["a1"], t["g1"]], 0).contiguous(),
+            "in": torch.cat([t["q"], t["k"], t["v"], t["a1"], t["g1"], t["b"]], 0).contiguous(),
             "conv": torch.cat([t["q_conv"], t["k_conv"], t["v_conv"]], 0).t().contiguous(),  # [taps, channels]
             "a2": t["a2"], "g2": t["g2"], "A_log": t["A_log"], "dt_bias": t["dt_bias"], "o": t["o"],
             "norm": t["norm"].repeat(self.heads).contiguous(),  # the heads share the weight; the kernel reads one per column
@@ -378,13 +378,13 @@ class ChannelDeltaRule(Part):
         w = self.w
         n = x.shape[0]
         state, conv_state = cache.states
-        u = project(x, w["in"])  # q | k | v | b | a1 | g1
+        u = project(x, w["in"])  # q | k | v | a1 | g1 | b
         qkv = torch.empty((n, self.channels), dtype=x.dtype, device=x.device)
         ops.causal_conv_silu(qkv, u, 0, w["conv"], None, conv_state, batch.seq_of_token, batch.q_start, batch.state_slot)
         if self.taps > 1:
             ops.conv_state_update(conv_state, u, 0, batch.q_start, batch.state_slot)
-        a = project(u[:, self.a_cols[0] : self.a_cols[1]].contiguous(), w["a2"])  # [n, heads * head_dim]
-        g = project(u[:, self.g_cols[0] : self.g_cols[1]].contiguous(), w["g2"])  # [n, heads * value_dim]
+        a = project(u[:, self.a_cols[0] : self.a_cols[1]], w["a2"])  # [n, heads * head_dim]; the library reads the column slice in place
+        g = project(u[:, self.g_cols[0] : self.g_cols[1]], w["g2"])  # [n, heads * value_dim]
         rows = torch.empty((n, _recurrence_row(self.kv_heads, self.heads, self.d, self.dv)), dtype=torch.float32, device=x.device)
         ops.channel_delta_prep(rows, qkv, u, self.b_col, a, w["dt_bias"], w["A_log"], self.heads, self.kv_heads, self.d, self.dv, self.unit_eps)
         o = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)

@@ -24,6 +24,7 @@ def test_trace_replay_with_four_state_slots(dtype, tmp_path):
     w = suite.make_model(tmp_path / "m", cfg, seed=41)
     seqs = {f"r{i}": suite.tokens_for(cfg, n, seed=80 + i) for i, n in enumerate((40, 33, 21, 38, 27, 30))}
     want = {r: plain.forward(cfg, w, t) for r, t in seqs.items()}
+    rounding = {r: suite.rounding_error(tmp_path / "m", "cuda:0", dtype, t, want[r]) for r, t in seqs.items()}
     run = TraceRun(tmp_path / "m", dtype, tmp_path / "out", max_tokens=4 * 64, page_size=8)
     at = {r: 0 for r in seqs}
     order = list(seqs)
@@ -44,7 +45,7 @@ def test_trace_replay_with_four_state_slots(dtype, tmp_path):
             for r, toks, _ in entries:
                 n = len(toks)
                 lo = at[r] - n
-                suite.close(got[row : row + n].astype(np.float64), want[r][lo : lo + n], dtype, f"{r} at {lo}")
+                suite.close(got[row : row + n].astype(np.float64), want[r][lo : lo + n], dtype, f"{r} at {lo}", rounding[r])
                 row += n
             live = [r for r in live if r not in end]
             step += 1
