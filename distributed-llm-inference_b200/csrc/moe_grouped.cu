@@ -1,6 +1,6 @@
 // The experts' products of a routed feed-forward for steps of many tokens (bfloat16): the (token, expert) pairs are
 // sorted by expert on the device (a counting sort; no shape depends on the data), and two grouped products run over the
-// sorted rows on the tensor cores (mma.sync m16n8k16, float32 sums), a tile of 64 rows belonging to one expert:
+// sorted rows on the tensor cores (mma.sync m16n8k16 fed by ldmatrix, float32 sums), a tile of 64 rows belonging to one expert:
 //   hidden[row] = act(gate_e x) * (up_e x)        (both sums rounded to bfloat16 first, as a stored product would be)
 //   partial[row] = down_e hidden[row]             (float32)
 //   out[t] = sum_k weights[t][k] * partial[row of pair (t, k)], in the order of k, float32, one rounding.
@@ -13,8 +13,9 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 32, PAD = 8, THREADS = 128;
-constexpr int LDS = BK + PAD;  // elements of a staged row: 80 bytes, so the eight rows a fragment load touches lie in different banks
+constexpr int BM = 64, BN = 64, BK = 64, PAD = 8, THREADS = 128, STAGES = 3;
+constexpr int LDS = BK + PAD;  // elements of a staged row: 144 bytes, so the eight rows of an 8 x 8 fragment lie in different banks
+constexpr int TILE_ELEMS = BM * LDS;  // one staged tile of 64 rows (A, or one of B's)
 
 // counts <- 0, and -1 into the tile and row maps (what no expert claims stays -1)
 __global__ void moe_init_kernel(int* __restrict__ counts, int n_counts, int* __restrict__ maps, int n_maps) {
@@ -38,7 +39,6 @@ __global__ void moe_count_kernel(const int* __restrict__ ids, int pairs, int* __
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets, int* __restrict__ tile_expert) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ int total;
   if (threadIdx.x == 0) {
     int at = 0;
     for (int e = 0; e < E; ++e) {
@@ -46,12 +46,10 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __re
       at += (counts[e] + BM - 1) / BM * BM;
     }
     offsets[E] = at;
-    total = at;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x)
     for (int tile = offsets[e] / BM; tile < offsets[e + 1] / BM; ++tile) tile_expert[tile] = e;
-  (void)total;
 }
 
 // pos[p]: the sorted row of pair p; row_pair[row]: the pair of a sorted row (-1 for padding: set by the caller beforehand)
@@ -87,9 +85,16 @@ __device__ __forceinline__ float glu_act(float g, int act) {
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
 // C[row][n] = sum_k A[src(row)][k] * B_e[n][k] over one tile of 64 sorted rows of expert e = tile_expert[tile] and 64 columns.
 // GLU: two B tiles (rows n and half + n of the expert's matrix) and C = act(first) * second, bfloat16; else C float32.
 // row_pair (GLU): the sorted row's pair, whose token pair / top is the row of A (-1: zeros); without it the row of A is the sorted row.
+// k-tiles of 64 arrive by asynchronous copies three stages deep (a step of few tokens only streams the experts' matrices, and
+// that is bound by the bytes in flight); fragments are read with ldmatrix.
 template <bool GLU>
 __global__ void __launch_bounds__(THREADS) moe_grouped_gemm_kernel(const bf16* __restrict__ A, long long a_stride, const int* __restrict__ row_pair,
                                                                    int top, const bf16* __restrict__ B, long long b_expert_stride, int half,
@@ -101,24 +106,23 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_gemm_kernel(const bf16* _
   const int e = tile_expert[tile_m];
   if (e < 0) return;
   constexpr int NB = GLU ? 2 : 1;
-  __shared__ __align__(16) bf16 As[2][BM][LDS];
-  __shared__ __align__(16) bf16 Bs[2][NB][BN][LDS];
+  constexpr int STAGE_ELEMS = (1 + NB) * TILE_ELEMS;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int wm = warp >> 1, wn = warp & 1;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * BN;
   const bf16* Be = B + (size_t)e * b_expert_stride;
 
-  // the two 16-byte chunks of A (and of each B tile) this thread copies per k-tile
-  const bf16* a_src[2];
-  const bf16* b_src[NB][2];
-  int cr[2], cc[2];
+  // the four 16-byte chunks of A (and of each B tile) this thread copies per k-tile: rows r0 + 16 i, one column of chunks
+  const int r0 = tid >> 3, cc = (tid & 7) * 8;
+  const bf16* a_src[4];
+  const bf16* b_src[NB][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int chunk = tid + i * THREADS;
-    cr[i] = chunk >> 2;
-    cc[i] = (chunk & 3) * 8;
-    const int row = tile_m * BM + cr[i];
+  for (int i = 0; i < 4; ++i) {
+    const int r = r0 + 16 * i;
+    const int row = tile_m * BM + r;
     if (row_pair) {
       const int p = row_pair[row];
       a_src[i] = p >= 0 ? A + (size_t)(p / top) * a_stride : nullptr;
@@ -126,19 +130,21 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_gemm_kernel(const bf16* _
       a_src[i] = A + (size_t)row * a_stride;
     }
 #pragma unroll
-    for (int j = 0; j < NB; ++j) b_src[j][i] = n0 + cr[i] < N ? Be + (size_t)(j * half + n0 + cr[i]) * K : nullptr;
+    for (int j = 0; j < NB; ++j) b_src[j][i] = n0 + r < N ? Be + (size_t)(j * half + n0 + r) * K : nullptr;
   }
 
   auto load = [&](int stage, int k0) {
+    bf16* As = smem + stage * STAGE_ELEMS;
+    const bool in_k = k0 + cc < K;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const bool in_k = k0 + cc[i] < K;
+    for (int i = 0; i < 4; ++i) {
+      const int r = r0 + 16 * i;
       const bool a_ok = in_k && a_src[i] != nullptr;
-      cp_async16(&As[stage][cr[i]][cc[i]], a_ok ? (const void*)(a_src[i] + k0 + cc[i]) : (const void*)A, a_ok ? 16 : 0);
+      cp_async16(As + r * LDS + cc, a_ok ? (const void*)(a_src[i] + k0 + cc) : (const void*)A, a_ok ? 16 : 0);
 #pragma unroll
       for (int j = 0; j < NB; ++j) {
         const bool b_ok = in_k && b_src[j][i] != nullptr;
-        cp_async16(&Bs[stage][j][cr[i]][cc[i]], b_ok ? (const void*)(b_src[j][i] + k0 + cc[i]) : (const void*)B, b_ok ? 16 : 0);
+        cp_async16(As + (1 + j) * TILE_ELEMS + r * LDS + cc, b_ok ? (const void*)(b_src[j][i] + k0 + cc) : (const void*)B, b_ok ? 16 : 0);
       }
     }
   };
@@ -154,38 +160,37 @@ __global__ void __launch_bounds__(THREADS) moe_grouped_gemm_kernel(const bf16* _
         for (int q = 0; q < 4; ++q) acc[j][mi][ni][q] = 0.f;
 
   const int k_tiles = (K + BK - 1) / BK;
-  load(0, 0);
-  cp_async_commit();
-  for (int kt = 0; kt < k_tiles; ++kt) {
-    const int stage = kt & 1;
-    if (kt + 1 < k_tiles) load(stage ^ 1, (kt + 1) * BK);
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < k_tiles) load(s, s * BK);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();  // k-tile kt has landed, and everyone is done with the stage that is filled next
+    const int next = kt + STAGES - 1;
+    if (next < k_tiles) load(next % STAGES, next * BK);
+    cp_async_commit();
+    const bf16* As = smem + (kt % STAGES) * STAGE_ELEMS;
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
       uint32_t a[2][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi) {
-        const int r = wm * 32 + mi * 16 + g;
-        a[mi][0] = *reinterpret_cast<const uint32_t*>(&As[stage][r][kk + 2 * t]);
-        a[mi][1] = *reinterpret_cast<const uint32_t*>(&As[stage][r + 8][kk + 2 * t]);
-        a[mi][2] = *reinterpret_cast<const uint32_t*>(&As[stage][r][kk + 2 * t + 8]);
-        a[mi][3] = *reinterpret_cast<const uint32_t*>(&As[stage][r + 8][kk + 2 * t + 8]);
-      }
+      for (int mi = 0; mi < 2; ++mi) ldmatrix_x4(a[mi], As + (wm * 32 + mi * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8);
 #pragma unroll
       for (int j = 0; j < NB; ++j)
 #pragma unroll
-        for (int ni = 0; ni < 4; ++ni) {
-          const int c = wn * 32 + ni * 8 + g;
-          uint32_t b[2];
-          b[0] = *reinterpret_cast<const uint32_t*>(&Bs[stage][j][c][kk + 2 * t]);
-          b[1] = *reinterpret_cast<const uint32_t*>(&Bs[stage][j][c][kk + 2 * t + 8]);
+        for (int p = 0; p < 2; ++p) {
+          uint32_t b4[4];
+          ldmatrix_x4(b4, As + (1 + j) * TILE_ELEMS + (wn * 32 + p * 16 + (lane & 7) + ((lane >> 4) << 3)) * LDS + kk + ((lane >> 3) & 1) * 8);
+          const uint32_t blo[2] = {b4[0], b4[1]}, bhi[2] = {b4[2], b4[3]};
 #pragma unroll
-          for (int mi = 0; mi < 2; ++mi) mma_bf16(acc[j][mi][ni], a[mi], b);
+          for (int mi = 0; mi < 2; ++mi) {
+            mma_bf16(acc[j][mi][2 * p], a[mi], blo);
+            mma_bf16(acc[j][mi][2 * p + 1], a[mi], bhi);
+          }
         }
     }
-    __syncthreads();  // the stage is overwritten by the copies issued next iteration
   }
   cp_async_wait<0>();
 
@@ -256,10 +261,19 @@ DLI_EXPORT int dli_moe_grouped(void* out, const void* x, const int* ids, const f
   if (e != cudaSuccess) return (int)e;
   e = launch_pdl((moe_scatter_kernel), dim3((pairs + 255) / 256), dim3(256), 0, stream, 1, ids, (const int*)rank, (const int*)offsets, pairs, pos, row_pair);
   if (e != cudaSuccess) return (int)e;
-  e = launch_pdl((moe_grouped_gemm_kernel<true>), dim3((ff + BN - 1) / BN, tiles), dim3(THREADS), 0, stream, 1, (const bf16*)x, (long long)W,
+  constexpr int SMEM_GLU = STAGES * 3 * TILE_ELEMS * (int)sizeof(bf16), SMEM_PLAIN = STAGES * 2 * TILE_ELEMS * (int)sizeof(bf16);
+  static OncePerDevice configured;
+  if (!configured.here()) {
+    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GLU);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PLAIN);
+    if (e != cudaSuccess) return (int)e;
+    configured.here() = true;
+  }
+  e = launch_pdl((moe_grouped_gemm_kernel<true>), dim3((ff + BN - 1) / BN, tiles), dim3(THREADS), SMEM_GLU, stream, 1, (const bf16*)x, (long long)W,
                  (const int*)row_pair, top, (const bf16*)w_gate_up, (long long)2 * ff * W, ff, hidden, (long long)ff, ff, W, (const int*)tile_expert, act);
   if (e != cudaSuccess) return (int)e;
-  e = launch_pdl((moe_grouped_gemm_kernel<false>), dim3((W + BN - 1) / BN, tiles), dim3(THREADS), 0, stream, 1, (const bf16*)hidden, (long long)ff,
+  e = launch_pdl((moe_grouped_gemm_kernel<false>), dim3((W + BN - 1) / BN, tiles), dim3(THREADS), SMEM_PLAIN, stream, 1, (const bf16*)hidden, (long long)ff,
                  (const int*)nullptr, top, (const bf16*)w_down, (long long)W * ff, 0, (void*)partial, (long long)W, W, ff, (const int*)tile_expert, 0);
   if (e != cudaSuccess) return (int)e;
   e = launch_pdl((moe_combine_kernel), dim3(n), dim3(W >= 1024 ? 256 : 128), 0, stream, 1, (bf16*)out, (const float*)partial, (const int*)pos, weights, W, top);

@@ -83,15 +83,15 @@ __global__ void channel_delta_prep_kernel(float* __restrict__ rows, const T* __r
   for (int i = threadIdx.x; i < heads; i += blockDim.x) row[L.b + i] = 1.f / (1.f + expf(-to_float(u[t * u_stride + b_col + i])));
 }
 
-constexpr int REC_R = 32;       // key rows of a state column that one thread keeps in registers
+constexpr int REC_R_MAX = 32;   // key rows of a state column that one thread keeps in registers: 32, 16 or 8 (the fewer, the more threads share a column)
 constexpr int REC_THREADS = 128;  // at most; a CTA has as many threads as its columns need
 constexpr int REC_TOKENS = 16;  // tokens staged in shared memory at a time, the next sixteen on their way meanwhile
 
-// Staged vectors are laid out in slices of REC_R floats, each followed by 4 floats of padding, so that the threads of a
+// Staged vectors are laid out in slices of R floats, each followed by 4 floats of padding, so that the threads of a
 // warp that hold different slices read different banks.
-__host__ __device__ inline int slice_at(int i) { return i + ((i / REC_R) << 2); }
-__host__ __device__ inline int staged_floats(int ks) { return ks * (REC_R + 4); }
-__host__ __device__ inline int token_floats(int ks, int cols) { return (3 * staged_floats(ks) + cols + 1 + 3) & ~3; }
+__host__ __device__ inline int slice_at(int i, int R) { return i + ((i / R) << 2); }
+__host__ __device__ inline int staged_floats(int ks, int R) { return ks * (R + 4); }
+__host__ __device__ inline int token_floats(int ks, int cols, int R) { return (3 * staged_floats(ks, R) + cols + 1 + 3) & ~3; }
 
 __device__ __forceinline__ void copy_async4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -103,12 +103,12 @@ __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_gr
 template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // One CTA: some value columns of one head of one sequence.  KS threads (consecutive lanes) share a column, each with
-// REC_R key rows of it in registers (rows beyond d are zeros).  MODE 0 (bonus): o = sum_i a_i (S_i + u_i k_i v);
+// R key rows of it in registers (rows beyond d are zeros).  MODE 0 (bonus): o = sum_i a_i (S_i + u_i k_i v);
 // S_i <- g_i S_i + k_i v.  MODE 1 (delta): S_i <- g_i S_i; w = beta (v - sum_i k_i S_i); S_i <- S_i + k_i w; o = sum_i a_i S_i.
 // state [slots][heads][dv][d] (a value column's key rows are contiguous).  Sums over the key rows are added in an
 // order fixed by d alone, token after token, so a result does not depend on how a sequence was cut into steps.
 // Tokens arrive by asynchronous copies, sixteen at a time, the next sixteen under way while these are walked.
-template <int MODE>
+template <int MODE, int REC_R>
 __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __restrict__ o, const float* __restrict__ rows,
                                                                        float* __restrict__ state, const int* __restrict__ q_start,
                                                                        const int* __restrict__ state_slot, const float* __restrict__ bonus,
@@ -121,8 +121,8 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
   if (t1 <= t0) return;
   const RowLayout L = row_layout(kq, heads, d, dv);
   const int kqh = head / (heads / kq);
-  const int dpad = staged_floats(ks);
-  const int tok_floats = token_floats(ks, cols_per_cta);  // per staged token: A | K | G | V of this CTA's columns | beta
+  const int dpad = staged_floats(ks, REC_R);
+  const int tok_floats = token_floats(ks, cols_per_cta, REC_R);  // per staged token: A | K | G | V of this CTA's columns | beta
   const int buf_floats = REC_TOKENS * tok_floats;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int col_local = tid / ks, slice = tid - col_local * ks;
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
         const int which = rem / chunks, i = (rem - which * chunks) << 2;
         const float* row = rows + (size_t)(base + tok) * L.stride;
         const float* src = which == 0 ? row + L.a + kqh * d + i : (which == 1 ? row + L.k + kqh * d + i : row + L.g + head * d + i);
-        copy_async16(dst0 + tok * tok_floats + which * dpad + slice_at(i), src);
+        copy_async16(dst0 + tok * tok_floats + which * dpad + slice_at(i, REC_R), src);
       }
     } else {
       for (int e = tid; e < cnt * 3 * d; e += nthreads) {
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
         const int which = rem / d, i = rem - which * d;
         const float* row = rows + (size_t)(base + tok) * L.stride;
         const float* src = which == 0 ? row + L.a + kqh * d + i : (which == 1 ? row + L.k + kqh * d + i : row + L.g + head * d + i);
-        copy_async4(dst0 + tok * tok_floats + which * dpad + slice_at(i), src);
+        copy_async4(dst0 + tok * tok_floats + which * dpad + slice_at(i, REC_R), src);
       }
     }
     const int extra = cols_per_cta + (MODE == 1 ? 1 : 0);
@@ -201,9 +201,9 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
     __syncthreads();
     const float* tile = sm + buf * buf_floats;
     for (int tok = 0; tok < cnt; ++tok) {
-      const float4* A = reinterpret_cast<const float4*>(tile + tok * tok_floats + slice_at(i0));
-      const float4* K = reinterpret_cast<const float4*>(tile + tok * tok_floats + dpad + slice_at(i0));
-      const float4* G = reinterpret_cast<const float4*>(tile + tok * tok_floats + 2 * dpad + slice_at(i0));
+      const float4* A = reinterpret_cast<const float4*>(tile + tok * tok_floats + slice_at(i0, REC_R));
+      const float4* K = reinterpret_cast<const float4*>(tile + tok * tok_floats + dpad + slice_at(i0, REC_R));
+      const float4* G = reinterpret_cast<const float4*>(tile + tok * tok_floats + 2 * dpad + slice_at(i0, REC_R));
       const float v = tile[tok * tok_floats + 3 * dpad + (col_local < cols_per_cta ? col_local : 0)];
       float acc4[4] = {0.f, 0.f, 0.f, 0.f};  // four running sums: the chain of dependent multiply-adds is a quarter as long
       if (MODE == 0) {
@@ -307,37 +307,42 @@ DLI_EXPORT int dli_channel_delta_prep(float* rows, const void* qkv, const void* 
 DLI_EXPORT int dli_decay_recurrence(float* o, const float* rows, float* state, const int* q_start, const int* state_slot, const float* bonus,
                                     int num_seqs, int heads, int kq, int d, int dv, int mode, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
-  if (heads < 1 || kq < 1 || heads % kq || d < 1 || dv < 1 || d > REC_R * 16 || (mode == 0 && !bonus) || mode < 0 || mode > 1 || heads > 65535 ||
+  if (heads < 1 || kq < 1 || heads % kq || d < 1 || dv < 1 || d > 512 || (mode == 0 && !bonus) || mode < 0 || mode > 1 || heads > 65535 ||
       num_seqs > 65535)
     return DLI_ERR_UNSUPPORTED;
-  int ks = 1;
-  while (ks * REC_R < d) ks <<= 1;
+  // Key rows a thread: 32 where there are warps enough (a decode step of many sequences); 16 or 8 where a few long sequences
+  // would leave the GPU idle, so that more threads share a column and a token's chain of multiply-adds gets shorter.
+  int R = REC_R_MAX;
+  auto lanes = [&](int r) { int k = 1; while (k * r < d) k <<= 1; return k; };
+  while (R > 8 && lanes(R / 2) <= 32 && (long long)num_seqs * heads * dv * lanes(R) / 32 < 4LL * sm_count()) R >>= 1;
+  const int ks = lanes(R);
+  if (ks > 32) return DLI_ERR_UNSUPPORTED;
   // columns a CTA: all that 128 threads hold, fewer while the grid would leave SMs idle (never under a warp's worth of threads)
   int cols = REC_THREADS / ks;
+  if (cols < 1) cols = 1;
   if (cols > dv) cols = dv;
   while (cols * ks > 32 && (long long)((dv + cols - 1) / cols) * heads * num_seqs < 2LL * sm_count()) cols = (cols + 1) / 2;
-  int threads = ((cols * ks + 31) / 32) * 32;
-  const size_t smem = (size_t)2 * REC_TOKENS * token_floats(ks, cols) * sizeof(float);
+  const int threads = ((cols * ks + 31) / 32) * 32;
+  const size_t smem = (size_t)2 * REC_TOKENS * token_floats(ks, cols, R) * sizeof(float);
+  if (smem > 227 * 1024) return DLI_ERR_UNSUPPORTED;
   const dim3 grid((dv + cols - 1) / cols, heads, num_seqs);
-  cudaError_t e;
-  if (mode == 0) {
-    static MaxPerDevice set;
-    if ((int)smem > 48 * 1024 && set.here() < (int)smem) {
-      e = cudaFuncSetAttribute(decay_recurrence_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      set.here() = (int)smem;
-    }
-    e = launch_pdl((decay_recurrence_kernel<0>), grid, dim3(threads), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, kq, d,
-                   dv, ks, cols);
-  } else {
-    static MaxPerDevice set;
-    if ((int)smem > 48 * 1024 && set.here() < (int)smem) {
-      e = cudaFuncSetAttribute(decay_recurrence_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-      set.here() = (int)smem;
-    }
-    e = launch_pdl((decay_recurrence_kernel<1>), grid, dim3(threads), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, kq, d,
-                   dv, ks, cols);
+  cudaError_t e = cudaSuccess;
+#define DLI_REC(MODE, RR)                                                                                                              \
+  {                                                                                                                                    \
+    static MaxPerDevice set;                                                                                                           \
+    if ((int)smem > 48 * 1024 && set.here() < (int)smem) {                                                                             \
+      e = cudaFuncSetAttribute(decay_recurrence_kernel<MODE, RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+      if (e != cudaSuccess) return (int)e;                                                                                             \
+      set.here() = (int)smem;                                                                                                          \
+    }                                                                                                                                  \
+    e = launch_pdl((decay_recurrence_kernel<MODE, RR>), grid, dim3(threads), smem, stream, 1, o, rows, state, q_start, state_slot, bonus, heads, \
+                   kq, d, dv, ks, cols);                                                                                               \
   }
+  if (mode == 0) {
+    if (R == 32) DLI_REC(0, 32) else if (R == 16) DLI_REC(0, 16) else DLI_REC(0, 8)
+  } else {
+    if (R == 32) DLI_REC(1, 32) else if (R == 16) DLI_REC(1, 16) else DLI_REC(1, 8)
+  }
+#undef DLI_REC
   return (int)e;
 }

@@ -29,9 +29,7 @@ SKINNY_MAX_TOKENS_HEAD = 64
 
 def decode_product(x: torch.Tensor, max_tokens: int = SKINNY_MAX_TOKENS) -> bool:
     """Whether a product with these activations goes to the engine's own decode kernel."""
-    # (TMA reads the activations: a column slice of one row is "contiguous" and yet may start off a 16-byte boundary)
-    return (x.dtype == torch.bfloat16 and x.shape[0] <= max_tokens and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
-            and x.is_contiguous() and x.data_ptr() % 16 == 0)
+    return x.dtype == torch.bfloat16 and x.shape[0] <= max_tokens and ops.skinny_gemm_supported(x.shape[0], x.shape[1])
 
 
 # Up to this many tokens the decode product also finishes the next elementwise step (rotary and
@@ -82,7 +80,9 @@ def project(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, max_t
     """y = x W^T for a step's tokens, in x's dtype or in ``out_dtype`` (float32 for logits).  x may be
     ops.ScaledRows (rows that still lack their norm's factor): those only exist for token counts that
     the decode kernel serves, which applies the factor."""
-    if isinstance(x, ops.ScaledRows) or decode_product(x, max_tokens):
+    # TMA reads the decode product's activations: rows back to back from a 16-byte boundary (a column slice of wider rows is
+    # neither, and a slice of a single row, though "contiguous", may start off the boundary): those stay with the library
+    if isinstance(x, ops.ScaledRows) or (decode_product(x, max_tokens) and x.is_contiguous() and x.data_ptr() % 16 == 0):
         return ops.skinny_gemm(x, weight, out_dtype or x.dtype)
     if out_dtype == torch.float32 and x.dtype != torch.float32:
         return logits_product(x, weight)

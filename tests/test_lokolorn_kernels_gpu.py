@@ -143,7 +143,9 @@ def test_decay_recurrence(mode, sizes):
         for t in range(int(q_start[s]), int(q_start[s + 1])):
             ops.decay_recurrence(o_one[t : t + 1], rows[t : t + 1].cuda(), s_one, _i32([0, 1]).cuda(), slots[s : s + 1].cuda(), kq, mode,
                                  None if bonus is None else bonus.cuda())
-    assert torch.equal(o_one, o_dev) and torch.equal(s_one, s_dev), "token by token differs from the portion"
+    # (equal up to float32 rounding: how many threads share a column, hence the order of a sum, follows the launch's shape)
+    _close(o_one, o_dev.cpu(), 1e-5, "token by token against the portion: o")
+    _close(s_one, s_dev.cpu(), 1e-5, "token by token against the portion: state")
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
