@@ -136,33 +136,35 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
   for (int e = tid; e < 2 * buf_floats; e += nthreads) sm[e] = 0.f;
   __syncthreads();
 
+  // A thread copies the same places of every token of a tile: where they lie is worked out once per place, not once per token.
   auto stage = [&](int buf, int base) {
     const int cnt = min(REC_TOKENS, t1 - base);
     float* dst0 = sm + buf * buf_floats;
+    const float* row0 = rows + (size_t)base * L.stride;
     if (vec) {
       const int chunks = d >> 2;
-      for (int e = tid; e < cnt * 3 * chunks; e += nthreads) {
-        const int tok = e / (3 * chunks), rem = e - tok * 3 * chunks;
-        const int which = rem / chunks, i = (rem - which * chunks) << 2;
-        const float* row = rows + (size_t)(base + tok) * L.stride;
-        const float* src = which == 0 ? row + L.a + kqh * d + i : (which == 1 ? row + L.k + kqh * d + i : row + L.g + head * d + i);
-        copy_async16(dst0 + tok * tok_floats + which * dpad + slice_at(i, REC_R), src);
+      for (int c = tid; c < 3 * chunks; c += nthreads) {
+        const int which = c / chunks, i = (c - which * chunks) << 2;
+        const float* src = row0 + (which == 0 ? L.a + kqh * d : (which == 1 ? L.k + kqh * d : L.g + head * d)) + i;
+        float* dst = dst0 + which * dpad + slice_at(i, REC_R);
+        for (int tok = 0; tok < cnt; ++tok) copy_async16(dst + tok * tok_floats, src + (size_t)tok * L.stride);
       }
     } else {
-      for (int e = tid; e < cnt * 3 * d; e += nthreads) {
-        const int tok = e / (3 * d), rem = e - tok * 3 * d;
-        const int which = rem / d, i = rem - which * d;
-        const float* row = rows + (size_t)(base + tok) * L.stride;
-        const float* src = which == 0 ? row + L.a + kqh * d + i : (which == 1 ? row + L.k + kqh * d + i : row + L.g + head * d + i);
-        copy_async4(dst0 + tok * tok_floats + which * dpad + slice_at(i, REC_R), src);
+      for (int c = tid; c < 3 * d; c += nthreads) {
+        const int which = c / d, i = c - which * d;
+        const float* src = row0 + (which == 0 ? L.a + kqh * d : (which == 1 ? L.k + kqh * d : L.g + head * d)) + i;
+        float* dst = dst0 + which * dpad + slice_at(i, REC_R);
+        for (int tok = 0; tok < cnt; ++tok) copy_async4(dst + tok * tok_floats, src + (size_t)tok * L.stride);
       }
     }
     const int extra = cols_per_cta + (MODE == 1 ? 1 : 0);
-    for (int e = tid; e < cnt * extra; e += nthreads) {
-      const int tok = e / extra, c = e - tok * extra;
-      const float* row = rows + (size_t)(base + tok) * L.stride;
-      if (c == cols_per_cta) copy_async4(dst0 + tok * tok_floats + 3 * dpad + c, row + L.b + head);
-      else if (col0 + c < dv) copy_async4(dst0 + tok * tok_floats + 3 * dpad + c, row + L.v + head * dv + col0 + c);
+    for (int c = tid; c < extra; c += nthreads) {
+      const float* src;
+      if (c == cols_per_cta) src = row0 + L.b + head;
+      else if (col0 + c < dv) src = row0 + L.v + head * dv + col0 + c;
+      else continue;
+      float* dst = dst0 + 3 * dpad + c;
+      for (int tok = 0; tok < cnt; ++tok) copy_async4(dst + tok * tok_floats, src + (size_t)tok * L.stride);
     }
   };
 
@@ -303,18 +305,22 @@ DLI_EXPORT int dli_channel_delta_prep(float* rows, const void* qkv, const void* 
   return (int)e;
 }
 
-// mode 0: bonus (needs `bonus` [heads][d]); mode 1: delta.  d up to 32 * 16.
+// mode 0: bonus (needs `bonus` [heads][d]); mode 1: delta.  d up to 512.  rows_per_lane: 32, 16 or 8 key rows a lane, or 0: chosen here.
 DLI_EXPORT int dli_decay_recurrence(float* o, const float* rows, float* state, const int* q_start, const int* state_slot, const float* bonus,
-                                    int num_seqs, int heads, int kq, int d, int dv, int mode, cudaStream_t stream) {
+                                    int num_seqs, int heads, int kq, int d, int dv, int mode, int rows_per_lane, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (heads < 1 || kq < 1 || heads % kq || d < 1 || dv < 1 || d > 512 || (mode == 0 && !bonus) || mode < 0 || mode > 1 || heads > 65535 ||
       num_seqs > 65535)
     return DLI_ERR_UNSUPPORTED;
-  // Key rows a thread: 32 where there are warps enough (a decode step of many sequences); 16 or 8 where a few long sequences
-  // would leave the GPU idle, so that more threads share a column and a token's chain of multiply-adds gets shorter.
+  // Key rows a thread: 32 where there are warps enough (a decode step of many sequences); for the bonus recurrence 16 or 8 where
+  // a few long sequences would leave the GPU idle, so that more threads share a column and a token's chain of multiply-adds
+  // gets shorter (one prompt of 4,096 tokens, 16 heads of 64 x 64: 1,512 us at 32, 1,238 at 16, 1,152 at 8).
   int R = REC_R_MAX;
   auto lanes = [&](int r) { int k = 1; while (k * r < d) k <<= 1; return k; };
-  while (R > 8 && lanes(R / 2) <= 32 && (long long)num_seqs * heads * dv * lanes(R) / 32 < 4LL * sm_count()) R >>= 1;
+  if (rows_per_lane == 32 || rows_per_lane == 16 || rows_per_lane == 8) R = rows_per_lane;
+  else if (rows_per_lane != 0) return DLI_ERR_UNSUPPORTED;
+  else if (mode == 0)  // (the delta rule adds two rounds of shuffles a token for every halving: measured, it is fastest at 32 everywhere)
+    while (R > 8 && lanes(R / 2) <= 32 && (long long)num_seqs * heads * dv * lanes(R) / 32 < 4LL * sm_count()) R >>= 1;
   const int ks = lanes(R);
   if (ks > 32) return DLI_ERR_UNSUPPORTED;
   // columns a CTA: all that 128 threads hold, fewer while the grid would leave SMs idle (never under a warp's worth of threads)

@@ -1533,7 +1533,7 @@ def channel_delta_prep(rows: torch.Tensor, qkv: torch.Tensor, u: torch.Tensor, b
 
 
 def decay_recurrence(o: torch.Tensor, rows: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, kq_heads: int,
-                     mode: str, bonus: torch.Tensor | None = None, max_len: int = 1 << 30) -> None:
+                     mode: str, bonus: torch.Tensor | None = None, max_len: int = 1 << 30, rows_per_lane: int = 0) -> None:
     """A linear recurrence over every sequence's tokens of this step, from and to its slot of ``state`` [slots, heads, dv, d] (float32; S
     transposed, so that a value column's d numbers are contiguous).  ``rows`` [n, decay_recurrence_row(...)] float32.  Per head, with
     a, k (of q/k head h // (heads / kq_heads)), decays g [d], values v [dv]:
@@ -1541,7 +1541,8 @@ def decay_recurrence(o: torch.Tensor, rows: torch.Tensor, state: torch.Tensor, q
     ``"bonus"``:  o = (S + diag(u) k v^T)^T a;   S <- diag(g) S + k v^T          (``bonus`` [heads, d]: u)
     ``"delta"``:  S <- diag(g) S;   w = beta (v - S^T k);   S <- S + k w^T;   o = S^T a
 
-    o [n, heads dv] float32.  Tokens are walked in order, the sums over d added in an order the sizes fix."""
+    o [n, heads dv] float32.  Tokens are walked in order.  ``rows_per_lane`` (32, 16, 8; 0: the launcher chooses from the step's shape):
+    how many key rows of a column one lane keeps, which fixes the order in which the sums over d are added."""
     _need(o, "o", torch.float32), _need(rows, "rows", torch.float32), _need(state, "state", torch.float32)
     _need(q_start, "q_start", torch.int32), _need(state_slot, "state_slot", torch.int32)
     _, heads, dv, d = state.shape
@@ -1555,9 +1556,9 @@ def decay_recurrence(o: torch.Tensor, rows: torch.Tensor, state: torch.Tensor, q
     if (kq_heads < 1 or heads % kq_heads or d > RECURRENCE_MAX_HEAD_DIM or tuple(o.shape) != (n, heads * dv) or rows.shape[1] != decay_recurrence_row(kq_heads, heads, d, dv)
             or q_start.numel() != state_slot.numel() + 1):
         raise KernelError(f"decay_recurrence: shapes do not agree (or the head size is above {RECURRENCE_MAX_HEAD_DIM})")
-    f = _fn("recurrence.cu", "dli_decay_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    f = _fn("recurrence.cu", "dli_decay_recurrence", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p])
     _check(f(_ptr(o), _ptr(rows), _ptr(state), _ptr(q_start), _ptr(state_slot), _ptr(bonus), state_slot.numel(), heads, kq_heads, d, dv,
-             0 if mode == "bonus" else 1, _stream()), "decay_recurrence")
+             0 if mode == "bonus" else 1, int(rows_per_lane), _stream()), "decay_recurrence")
 
 
 # ------------------------------------------------------------------ routed mixture of gated feed-forwards

@@ -675,7 +675,7 @@ def channel_delta_prep(rows, qkv, u, b_col, a, dt_bias, a_log, heads, kv_heads, 
     rows[:, ob : ob + heads] = torch.sigmoid(u[:, b_col : b_col + heads].float())
 
 
-def decay_recurrence(o, rows, state, q_start, state_slot, kq_heads, mode, bonus=None, max_len=0):
+def decay_recurrence(o, rows, state, q_start, state_slot, kq_heads, mode, bonus=None, max_len=0, rows_per_lane=0):
     _, heads, dv, d = state.shape  # the state is kept transposed: [slot, head, value column, key row]
     oa, ok, og, ov, ob = _row_offsets(kq_heads, heads, d, dv)
     fan = heads // kq_heads

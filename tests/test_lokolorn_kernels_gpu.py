@@ -112,11 +112,12 @@ def test_convolution_without_activation_and_sigmoid_gate(dtype, tol):
             _close(got, want, tol, f"norm gate={gate} {inner}")
 
 
+@pytest.mark.parametrize("lane_rows", [0, 8, 16, 32])
 @pytest.mark.parametrize("mode", ["bonus", "delta"])
 @pytest.mark.parametrize("sizes", [(4, 2, 12, 10), (2, 2, 32, 32), (3, 1, 9, 7), (2, 1, 64, 48), (2, 2, 128, 128), (1, 1, 136, 40), (2, 1, 72, 72)])
-def test_decay_recurrence(mode, sizes):
+def test_decay_recurrence(mode, sizes, lane_rows):
     """Portions of 1, 19 and 3 tokens from states that are not zero, in scattered slots; the state afterwards; then the same tokens
-    one at a time."""
+    one at a time; with 8, 16 and 32 key rows a lane, and with what the launcher chooses."""
     heads, kq, d, dv = sizes
     if mode == "bonus":
         kq, dv = heads, d
@@ -135,14 +136,14 @@ def test_decay_recurrence(mode, sizes):
     o_ref, o_dev = torch.zeros(n, heads * dv), torch.zeros(n, heads * dv, device="cuda")
     s_ref, s_dev = state.clone(), state.cuda()
     ref.decay_recurrence(o_ref, rows, s_ref, q_start, slots, kq, mode, bonus)
-    ops.decay_recurrence(o_dev, rows.cuda(), s_dev, q_start.cuda(), slots.cuda(), kq, mode, None if bonus is None else bonus.cuda())
+    ops.decay_recurrence(o_dev, rows.cuda(), s_dev, q_start.cuda(), slots.cuda(), kq, mode, None if bonus is None else bonus.cuda(), rows_per_lane=lane_rows)
     _close(o_dev, o_ref, 1e-4, "o")
     _close(s_dev, s_ref, 1e-4, "state")
     s_one, o_one = state.cuda(), torch.zeros(n, heads * dv, device="cuda")
     for s in range(3):
         for t in range(int(q_start[s]), int(q_start[s + 1])):
             ops.decay_recurrence(o_one[t : t + 1], rows[t : t + 1].cuda(), s_one, _i32([0, 1]).cuda(), slots[s : s + 1].cuda(), kq, mode,
-                                 None if bonus is None else bonus.cuda())
+                                 None if bonus is None else bonus.cuda(), rows_per_lane=lane_rows)
     # (equal up to float32 rounding: how many threads share a column, hence the order of a sum, follows the launch's shape)
     _close(o_one, o_dev.cpu(), 1e-5, "token by token against the portion: o")
     _close(s_one, s_dev.cpu(), 1e-5, "token by token against the portion: state")
