@@ -16,6 +16,7 @@ namespace {
 constexpr int BM = 64, BN = 64, BK = 64, PAD = 8, THREADS = 128, STAGES = 3;
 constexpr int LDS = BK + PAD;  // elements of a staged row: 144 bytes, so the eight rows of an 8 x 8 fragment lie in different banks
 constexpr int TILE_ELEMS = BM * LDS;  // one staged tile of 64 rows (A, or one of B's)
+constexpr int SORT_SMALL_MAX_PAIRS = 2048;  // up to here one block sorts the pairs in one launch
 
 // counts <- 0, and -1 into the tile and row maps (what no expert claims stays -1)
 __global__ void moe_init_kernel(int* __restrict__ counts, int n_counts, int* __restrict__ maps, int n_maps) {
@@ -62,6 +63,42 @@ __global__ void moe_scatter_kernel(const int* __restrict__ ids, const int* __res
   const int row = offsets[ids[p]] + rank[p];
   pos[p] = row;
   row_pair[row] = p;
+}
+
+// The whole sort in one block, for steps of few pairs (a decode step): maps to -1, counts and ranks in shared memory, offsets,
+// tile map, scatter.  One launch instead of four.
+__global__ void moe_sort_small_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ offsets, int* __restrict__ pos,
+                                      int* __restrict__ tile_expert, int tiles, int* __restrict__ row_pair) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int sh[];  // counts [E] | offsets [E + 1]
+  int* cnt = sh;
+  int* off = sh + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  for (int i = threadIdx.x; i < tiles; i += blockDim.x) tile_expert[i] = -1;
+  for (int i = threadIdx.x; i < tiles * BM; i += blockDim.x) row_pair[i] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) pos[p] = atomicAdd(&cnt[ids[p]], 1);  // the pair's rank for now
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = at;
+      at += (cnt[e] + BM - 1) / BM * BM;
+    }
+    off[E] = at;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    offsets[e] = off[e];
+    if (e < E)
+      for (int tile = off[e] / BM; tile < off[e + 1] / BM; ++tile) tile_expert[tile] = e;
+  }
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int row = off[ids[p]] + pos[p];
+    pos[p] = row;
+    row_pair[row] = p;
+  }
 }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
@@ -251,16 +288,23 @@ DLI_EXPORT int dli_moe_grouped(void* out, const void* x, const int* ids, const f
   int* pos = rank + pairs;
   int* tile_expert = pos + pairs;
   int* row_pair = tile_expert + tiles;
-  const int n_maps = tiles + tiles * BM;
-  cudaError_t e = launch_pdl((moe_init_kernel), dim3((E + 1 + n_maps + 255) / 256 < 1024 ? (E + 1 + n_maps + 255) / 256 : 1024), dim3(256), 0, stream, 1,
-                             counts, E + 1, tile_expert, n_maps);
-  if (e != cudaSuccess) return (int)e;
-  e = launch_pdl((moe_count_kernel), dim3((pairs + 255) / 256), dim3(256), 0, stream, 1, ids, pairs, counts, rank);
-  if (e != cudaSuccess) return (int)e;
-  e = launch_pdl((moe_plan_kernel), dim3(1), dim3(256), 0, stream, 1, (const int*)counts, E, offsets, tile_expert);
-  if (e != cudaSuccess) return (int)e;
-  e = launch_pdl((moe_scatter_kernel), dim3((pairs + 255) / 256), dim3(256), 0, stream, 1, ids, (const int*)rank, (const int*)offsets, pairs, pos, row_pair);
-  if (e != cudaSuccess) return (int)e;
+  cudaError_t e;
+  if (pairs <= SORT_SMALL_MAX_PAIRS && (2 * E + 1) * sizeof(int) <= 48 * 1024) {
+    e = launch_pdl((moe_sort_small_kernel), dim3(1), dim3(256), (size_t)(2 * E + 1) * sizeof(int), stream, 1, ids, pairs, E, offsets, pos, tile_expert, tiles,
+                   row_pair);
+    if (e != cudaSuccess) return (int)e;
+  } else {
+    const int n_maps = tiles + tiles * BM;
+    e = launch_pdl((moe_init_kernel), dim3((E + 1 + n_maps + 255) / 256 < 1024 ? (E + 1 + n_maps + 255) / 256 : 1024), dim3(256), 0, stream, 1, counts, E + 1,
+                   tile_expert, n_maps);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl((moe_count_kernel), dim3((pairs + 255) / 256), dim3(256), 0, stream, 1, ids, pairs, counts, rank);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl((moe_plan_kernel), dim3(1), dim3(256), 0, stream, 1, (const int*)counts, E, offsets, tile_expert);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl((moe_scatter_kernel), dim3((pairs + 255) / 256), dim3(256), 0, stream, 1, ids, (const int*)rank, (const int*)offsets, pairs, pos, row_pair);
+    if (e != cudaSuccess) return (int)e;
+  }
   constexpr int SMEM_GLU = STAGES * 3 * TILE_ELEMS * (int)sizeof(bf16), SMEM_PLAIN = STAGES * 2 * TILE_ELEMS * (int)sizeof(bf16);
   static OncePerDevice configured;
   if (!configured.here()) {

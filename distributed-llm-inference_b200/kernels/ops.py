@@ -1618,7 +1618,7 @@ def moe_experts(out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: 
         g = _fn("moe_grouped.cu", "dli_moe_grouped", [c_void_p] * 9 + [c_int] * 6 + [c_void_p])
         _check(g(_ptr(out), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), _ptr(ints), _ptr(hidden), _ptr(partial), n, W, ff, E, top,
                  GLU_ACTIVATIONS[activation], _stream()), "moe_experts")
-        launch_count += 6  # seven kernels a call
+        launch_count += 3 if n * top <= 2048 else 6  # four kernels a call (one block sorts up to 2,048 pairs), else seven
         return
     f = _fn("moe.cu", "dli_moe_pairs", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
     step = max(1, min(MOE_PAIR_CHUNK, 65535 // top))
