@@ -13,7 +13,7 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 64, PAD = 8, THREADS = 128, STAGES = 3;
+constexpr int BM = 64, BN = 64, BK = 64, PAD = 8, THREADS = 128;
 constexpr int LDS = BK + PAD;  // elements of a staged row: 144 bytes, so the eight rows of an 8 x 8 fragment lie in different banks
 constexpr int TILE_ELEMS = BM * LDS;  // one staged tile of 64 rows (A, or one of B's)
 constexpr int SORT_SMALL_MAX_PAIRS = 2048;  // up to here one block sorts the pairs in one launch
@@ -130,9 +130,9 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
 // C[row][n] = sum_k A[src(row)][k] * B_e[n][k] over one tile of 64 sorted rows of expert e = tile_expert[tile] and 64 columns.
 // GLU: two B tiles (rows n and half + n of the expert's matrix) and C = act(first) * second, bfloat16; else C float32.
 // row_pair (GLU): the sorted row's pair, whose token pair / top is the row of A (-1: zeros); without it the row of A is the sorted row.
-// k-tiles of 64 arrive by asynchronous copies three stages deep (a step of few tokens only streams the experts' matrices, and
-// that is bound by the bytes in flight); fragments are read with ldmatrix.
-template <bool GLU>
+// k-tiles of 64 arrive by asynchronous copies STAGES deep: three for a step of few tokens, which only streams the experts' matrices
+// and is bound by the bytes in flight; two for many tokens, where more CTAs an SM hide more latency.  Fragments are read with ldmatrix.
+template <bool GLU, int STAGES>
 __global__ void __launch_bounds__(THREADS) moe_grouped_gemm_kernel(const bf16* __restrict__ A, long long a_stride, const int* __restrict__ row_pair,
                                                                    int top, const bf16* __restrict__ B, long long b_expert_stride, int half,
                                                                    void* __restrict__ C, long long c_stride, int N, int K,
@@ -273,9 +273,9 @@ DLI_EXPORT int dli_moe_grouped_tiles(int pairs, int E) { return (pairs < E ? pai
 DLI_EXPORT int dli_moe_grouped_tile_rows() { return BM; }
 
 // ints: scratch of E + 1 (counts) + E + 1 (offsets) + 2 pairs (rank, pos) + tiles (tile_expert) + tiles * BM (row_pair) ints;
-// hidden: [tiles * BM][ff] bfloat16; partial: [tiles * BM][W] float32.
+// hidden: [tiles * BM][ff] bfloat16; partial: [tiles * BM][W] float32.  stages: 2 or 3 deep copies, or 0: chosen here.
 DLI_EXPORT int dli_moe_grouped(void* out, const void* x, const int* ids, const float* weights, const void* w_gate_up, const void* w_down, int* ints,
-                               void* hidden, float* partial, int n, int W, int ff, int E, int top, int act, cudaStream_t stream) {
+                               void* hidden, float* partial, int n, int W, int ff, int E, int top, int act, int stages, cudaStream_t stream) {
   if (n == 0) return 0;
   if (W < 8 || ff < 8 || (W % 8) || (ff % 8) || E < 1 || top < 1 || ((((uintptr_t)x) | ((uintptr_t)w_gate_up) | ((uintptr_t)w_down) | ((uintptr_t)hidden)) & 15))
     return DLI_ERR_UNSUPPORTED;
@@ -305,20 +305,34 @@ DLI_EXPORT int dli_moe_grouped(void* out, const void* x, const int* ids, const f
     e = launch_pdl((moe_scatter_kernel), dim3((pairs + 255) / 256), dim3(256), 0, stream, 1, ids, (const int*)rank, (const int*)offsets, pairs, pos, row_pair);
     if (e != cudaSuccess) return (int)e;
   }
-  constexpr int SMEM_GLU = STAGES * 3 * TILE_ELEMS * (int)sizeof(bf16), SMEM_PLAIN = STAGES * 2 * TILE_ELEMS * (int)sizeof(bf16);
+  constexpr int TILE_BYTES = TILE_ELEMS * (int)sizeof(bf16);
   static OncePerDevice configured;
   if (!configured.here()) {
-    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_GLU);
+    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 3 * TILE_BYTES);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_PLAIN);
+    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * 2 * TILE_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 3 * TILE_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(moe_grouped_gemm_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 2 * TILE_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured.here() = true;
   }
-  e = launch_pdl((moe_grouped_gemm_kernel<true>), dim3((ff + BN - 1) / BN, tiles), dim3(THREADS), SMEM_GLU, stream, 1, (const bf16*)x, (long long)W,
-                 (const int*)row_pair, top, (const bf16*)w_gate_up, (long long)2 * ff * W, ff, hidden, (long long)ff, ff, W, (const int*)tile_expert, act);
-  if (e != cudaSuccess) return (int)e;
-  e = launch_pdl((moe_grouped_gemm_kernel<false>), dim3((W + BN - 1) / BN, tiles), dim3(THREADS), SMEM_PLAIN, stream, 1, (const bf16*)hidden, (long long)ff,
-                 (const int*)nullptr, top, (const bf16*)w_down, (long long)W * ff, 0, (void*)partial, (long long)W, W, ff, (const int*)tile_expert, 0);
+  const int deep = stages == 2 || stages == 3 ? stages : (pairs > 16 * E ? 2 : 3);  // many rows an expert: the products bound the time, not the stream
+  const dim3 grid_up((ff + BN - 1) / BN, tiles), grid_down((W + BN - 1) / BN, tiles);
+  if (deep == 3) {
+    e = launch_pdl((moe_grouped_gemm_kernel<true, 3>), grid_up, dim3(THREADS), 3 * 3 * TILE_BYTES, stream, 1, (const bf16*)x, (long long)W, (const int*)row_pair, top,
+                   (const bf16*)w_gate_up, (long long)2 * ff * W, ff, hidden, (long long)ff, ff, W, (const int*)tile_expert, act);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl((moe_grouped_gemm_kernel<false, 3>), grid_down, dim3(THREADS), 3 * 2 * TILE_BYTES, stream, 1, (const bf16*)hidden, (long long)ff,
+                   (const int*)nullptr, top, (const bf16*)w_down, (long long)W * ff, 0, (void*)partial, (long long)W, W, ff, (const int*)tile_expert, 0);
+  } else {
+    e = launch_pdl((moe_grouped_gemm_kernel<true, 2>), grid_up, dim3(THREADS), 2 * 3 * TILE_BYTES, stream, 1, (const bf16*)x, (long long)W, (const int*)row_pair, top,
+                   (const bf16*)w_gate_up, (long long)2 * ff * W, ff, hidden, (long long)ff, ff, W, (const int*)tile_expert, act);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl((moe_grouped_gemm_kernel<false, 2>), grid_down, dim3(THREADS), 2 * 2 * TILE_BYTES, stream, 1, (const bf16*)hidden, (long long)ff,
+                   (const int*)nullptr, top, (const bf16*)w_down, (long long)W * ff, 0, (void*)partial, (long long)W, W, ff, (const int*)tile_expert, 0);
+  }
   if (e != cudaSuccess) return (int)e;
   e = launch_pdl((moe_combine_kernel), dim3(n), dim3(W >= 1024 ? 256 : 128), 0, stream, 1, (bf16*)out, (const float*)partial, (const int*)pos, weights, W, top);
   return (int)e;

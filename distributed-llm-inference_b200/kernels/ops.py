@@ -1594,10 +1594,11 @@ def moe_route(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router:
 
 
 def moe_experts(out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                activation: str = "silu") -> None:
+                activation: str = "silu", stages: int = 0) -> None:
     """out[t] = sum_k weights[t, k] * down_e(act(gate_e x[t]) * (up_e x[t])), e = ids[t, k], added in the order of k in float32.
     w_gate_up [E, 2 ff, W] (an expert's gate rows, then its up rows), w_down [E, W, ff].  The two inner sums are rounded to the
-    activation dtype before the activation, and so is their product."""
+    activation dtype before the activation, and so is their product.  ``stages`` (2, 3; 0: chosen from the step's shape): how deep
+    the grouped products' asynchronous copies run."""
     _need(out, "out"), _need(x, "x", out.dtype), _need(ids, "ids", torch.int32), _need(weights, "weights", torch.float32)
     _need(w_gate_up, "w_gate_up", out.dtype), _need(w_down, "w_down", out.dtype)
     n, W = x.shape
@@ -1615,9 +1616,9 @@ def moe_experts(out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: 
         ints = torch.empty(2 * (E + 1) + 2 * n * top + tiles + rows, dtype=torch.int32, device=out.device)
         hidden = torch.empty((rows, ff), dtype=out.dtype, device=out.device)
         partial = torch.empty((rows, W), dtype=torch.float32, device=out.device)
-        g = _fn("moe_grouped.cu", "dli_moe_grouped", [c_void_p] * 9 + [c_int] * 6 + [c_void_p])
+        g = _fn("moe_grouped.cu", "dli_moe_grouped", [c_void_p] * 9 + [c_int] * 7 + [c_void_p])
         _check(g(_ptr(out), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), _ptr(ints), _ptr(hidden), _ptr(partial), n, W, ff, E, top,
-                 GLU_ACTIVATIONS[activation], _stream()), "moe_experts")
+                 GLU_ACTIVATIONS[activation], int(stages), _stream()), "moe_experts")
         launch_count += 3 if n * top <= 2048 else 6  # four kernels a call (one block sorts up to 2,048 pairs), else seven
         return
     f = _fn("moe.cu", "dli_moe_pairs", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])

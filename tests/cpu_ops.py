@@ -726,7 +726,7 @@ def _glu_act(g, activation):
     return _silu(g)
 
 
-def moe_experts(out, x, ids, weights, w_gate_up, w_down, activation="silu"):
+def moe_experts(out, x, ids, weights, w_gate_up, w_down, activation="silu", stages=0):
     n, top = ids.shape
     ff = w_gate_up.shape[1] // 2
     acc = torch.zeros((n, x.shape[1]))

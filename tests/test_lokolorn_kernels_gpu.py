@@ -52,8 +52,9 @@ def test_add_rmsnorm_scaled(dtype, tol, H):
 
 
 @pytest.mark.parametrize("dtype,tol", DTYPES)
-def test_concat_rows_and_token_shift(dtype, tol):
-    n, W, V = 9, 52, 30
+@pytest.mark.parametrize("W", [52, 64, 1032])
+def test_concat_rows_and_token_shift(dtype, tol, W):
+    n, V = 9, 30
     h, table, ids = _rand(n, W, seed=1), _rand(V, W, seed=2).to(dtype), _i32([3, 29, 0, 7, 7, 1, 12, 5, 28])
     want, got = torch.empty(n, 2 * W, dtype=dtype), torch.empty(n, 2 * W, dtype=dtype, device="cuda")
     ref.concat_stream_rows(want, h, table, ids)
@@ -186,8 +187,9 @@ def test_routed_feed_forward(dtype, tol, sizes):
         _close(w_dev.cpu()[same], w_ref[same], 1e-5, "weights")
         out_ref, out_dev = torch.zeros(n, W, dtype=dtype), torch.zeros(n, W, dtype=dtype, device="cuda")
         ref.moe_experts(out_ref, x, ids_dev.cpu(), w_dev.cpu(), wgu, wd, "silu")
-        ops.moe_experts(out_dev, x.cuda(), ids_dev, w_dev, wgu.cuda(), wd.cuda(), "silu")
-        _close(out_dev, out_ref, tol, f"experts, {n} tokens")
+        for stages in (0, 2, 3):
+            ops.moe_experts(out_dev, x.cuda(), ids_dev, w_dev, wgu.cuda(), wd.cuda(), "silu", stages=stages)
+            _close(out_dev, out_ref, tol, f"experts, {n} tokens, copies {stages} deep")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
