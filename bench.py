@@ -859,7 +859,7 @@ def lokolorn_sizes(width, heads, kv_heads, dim, rec_heads, rec_dim, delta_heads,
                                                           "decay_rank": 64, "gate_rank": 64}}
     lat = {"type": "latent_attention", "mlp": mlp(), "mixer": {
         "heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": dim, "kv_rank": kv_rank, "scale": (dim + rot_dim) ** -0.5, "mask": {"size": window},
-        "rot": {"base": 500000.0, "dims": rot_dim, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+        "rot": {"base": 500000.0, "dims": rot_dim, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
     lk = {"architecture": "Lokolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": [par, dl, lat, dl],
           "loop": {"start": 0, "stop": 4, "times": 2}}
     sugonex, _ = sugonex_sizes(width=width, ff=ff, vocab=vocab, **sg)

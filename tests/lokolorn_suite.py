@@ -23,7 +23,7 @@ from tests.pazenex_suite import TOL, Session, close
 from tests.plain import lokolorn_plain as plain
 
 
-def parallel(heads=4, kv_heads=2, dim=16, vdim=8, conv=3, scale=0.7, rot_dims=8, base=100.0, r_heads=2, r_dim=12, rank=6, left_scale=0.8, right_scale=0.6):
+def parallel(heads=4, kv_heads=2, dim=16, vdim=8, conv=3, scale=0.7, rot_dims=8, base=100.0, r_heads=2, r_dim=12, rank=6, left_scale=0.9, right_scale=0.6):
     left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "scale": scale}
     if rot_dims:
         left["rot"] = {"base": base, "dims": rot_dims}
@@ -48,7 +48,7 @@ def latent(heads=3, dim=16, rot_dim=8, vdim=24, kv_rank=40, scale=0.6, base=1000
     return {"type": "latent_attention", "mixer": m}
 
 
-def moe(ff=20, experts=6, top=2, scale=1.5, groups=(3, 2)):
+def moe(ff=20, experts=6, top=2, scale=1.25, groups=(3, 2)):
     router = {"experts": experts, "top": top, "scale": scale}
     if groups:
         router["groups"] = {"count": groups[0], "keep": groups[1]}
@@ -73,7 +73,7 @@ CONFIGS = {
     "loop_from_start": config([delta(heads=3, kv_heads=1, dim=20, vdim=10, conv=2), parallel(heads=2, kv_heads=1, dim=8, vdim=24, conv=2, rot_dims=8, r_heads=3, r_dim=8)],
                               width=40, mlp=moe(ff=16, experts=4, top=1, groups=None), loop=(0, 2, 2), no_mlp=(0,)),
     "no_loop": config([latent(heads=4, dim=32, rot_dim=32, vdim=32, kv_rank=96, scale=0.3, window=None), parallel(heads=4, kv_heads=4, dim=16, vdim=16, conv=1, rot_dims=0),
-                       delta(heads=2, kv_heads=1, dim=64, vdim=32, conv=1)], width=64, vocab=130, mlp=moe(ff=64, experts=8, top=4, groups=(2, 1)), no_mlp=(2,)),
+                       delta(heads=2, kv_heads=1, dim=64, vdim=32, conv=1)], width=64, vocab=130, mlp=moe(ff=64, experts=12, top=4, groups=(3, 1)), no_mlp=(2,)),
     "loop_once": config([delta(), latent(heads=1, dim=16, rot_dim=0, vdim=48, kv_rank=20, window=5)], loop=(1, 2, 1), eps=1e-6,
                         mlp=moe(ff=24, experts=5, top=5, groups=None, scale=1.0)),
     "only_parallel": config([parallel(), parallel(heads=3, kv_heads=1, dim=32, vdim=32, conv=4, rot_dims=32, r_heads=1, r_dim=40)], loop=(0, 2, 2)),
@@ -210,7 +210,7 @@ def case_each_mechanism_alone(tmp_path, device, dtype):
     layers = {
         "attention_half": parallel(right_scale=0.0),
         "recurrence_half": parallel(left_scale=0.0, r_heads=3, r_dim=20),
-        "attention_rows_64": parallel(heads=4, kv_heads=1, dim=64, vdim=32, conv=4, rot_dims=64, right_scale=0.1),
+        "attention_rows_64": parallel(heads=4, kv_heads=2, dim=64, vdim=48, conv=3, rot_dims=64, right_scale=0.1),
         "attention_values_longer": parallel(heads=2, kv_heads=2, dim=16, vdim=48, conv=2, rot_dims=4),
         "attention_rows_128": parallel(heads=2, kv_heads=1, dim=128, vdim=128, conv=3, rot_dims=32, r_heads=1, r_dim=64),
         "recurrence_wide": parallel(left_scale=0.2, r_heads=2, r_dim=72, rank=8),

@@ -31,7 +31,7 @@ def test_run_order_follows_the_loop():
 def test_configuration_is_checked():
     good = suite.CONFIGS["mixed_loop"]
     parsed = LokolornConfig.from_dict(good)
-    assert isinstance(parsed, LokolornConfig) and parsed.layers[2].mixer.window == 13 and parsed.layers[0].mixer.left_scale == 0.8
+    assert isinstance(parsed, LokolornConfig) and parsed.layers[2].mixer.window == 13 and parsed.layers[0].mixer.left_scale == 0.9
     assert parsed.layers[0].mlp.group_count == 3 and parsed.layers[0].mlp.group_keep == 2 and parsed.layers[2].mixer.rot.scaling[0] == 4.0
     for path, value in ((("layers", 1, "mixer", "kv_heads"), 3), (("layers", 2, "mixer", "rot", "dims"), 7), (("layers", 2, "mixer", "rot", "dims"), 10),
                         (("layers", 0, "type"), "other"), (("loop", "stop"), 9), (("loop", "times"), 0), (("layers", 0, "mlp", "kind"), "dense"),
