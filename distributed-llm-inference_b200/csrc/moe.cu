@@ -9,7 +9,7 @@ using namespace dli;
 
 namespace {
 
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 512;  // sixteen warps: an expert's row each, side by side (a step of few tokens is a handful of blocks)
 constexpr int MAX_TOP = 32;
 
 // sum_i w[i] * xs[i] over a warp (xs: the token's row as floats in shared memory); 16-byte loads when `vec`
