@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(REC_THREADS) decay_recurrence_kernel(float* __
     copy_wait<1>();
     __syncthreads();
     const float* tile = sm + buf * buf_floats;
+#pragma unroll 2
     for (int tok = 0; tok < cnt; ++tok) {
       const float4* A = reinterpret_cast<const float4*>(tile + tok * tok_floats + slice_at(i0, REC_R));
       const float4* K = reinterpret_cast<const float4*>(tile + tok * tok_floats + dpad + slice_at(i0, REC_R));
