@@ -9,7 +9,7 @@ using namespace dli;
 
 namespace {
 
-constexpr int ROUTE_THREADS = 512;  // sixteen warps: an expert's row each, side by side (a step of few tokens is a handful of blocks)
+constexpr int ROUTE_THREADS = 512;  // at most: sixteen warps, an expert's row each, for a step of few tokens (a handful of blocks); four warps a token for many
 constexpr int MAX_TOP = 32;
 
 // sum_i w[i] * xs[i] over a warp (xs: the token's row as floats in shared memory); 16-byte loads when `vec`
@@ -47,10 +47,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(int* __restric
   __shared__ int picked[MAX_TOP];
   const size_t t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < W; i += ROUTE_THREADS) xs[i] = to_float(x[t * W + i]);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) xs[i] = to_float(x[t * W + i]);
   __syncthreads();
   const bool vec = (W % 8) == 0 && (((uintptr_t)router) & 15) == 0;
-  for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+  for (int e = warp; e < E; e += blockDim.x >> 5) {
     const float z = warp_dot<float>(router + (size_t)e * W, xs, W, lane, vec);
     if (lane == 0) {
       const float s = 1.f / (1.f + expf(-z));
@@ -199,16 +199,17 @@ DLI_EXPORT int dli_moe_route(int* ids, float* weights, const void* x, const floa
     return DLI_ERR_UNSUPPORTED;
   const size_t smem = ((size_t)W + 2 * E + groups) * sizeof(float);
   if (smem > 200 * 1024) return DLI_ERR_UNSUPPORTED;
+  const int threads = n <= 256 ? ROUTE_THREADS : 128;
   cudaError_t e;
   if (dtype == DLI_F32) {
     static MaxPerDevice set;
     if ((e = allow_smem(moe_route_kernel<float>, smem, set)) != cudaSuccess) return (int)e;
-    e = launch_pdl((moe_route_kernel<float>), dim3(n), dim3(ROUTE_THREADS), smem, stream, 1, ids, weights, (const float*)x, router, correction, W, E,
+    e = launch_pdl((moe_route_kernel<float>), dim3(n), dim3(threads), smem, stream, 1, ids, weights, (const float*)x, router, correction, W, E,
                    top, groups, keep, scale);
   } else {
     static MaxPerDevice set;
     if ((e = allow_smem(moe_route_kernel<__nv_bfloat16>, smem, set)) != cudaSuccess) return (int)e;
-    e = launch_pdl((moe_route_kernel<__nv_bfloat16>), dim3(n), dim3(ROUTE_THREADS), smem, stream, 1, ids, weights, (const __nv_bfloat16*)x, router,
+    e = launch_pdl((moe_route_kernel<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, 1, ids, weights, (const __nv_bfloat16*)x, router,
                    correction, W, E, top, groups, keep, scale);
   }
   return (int)e;
