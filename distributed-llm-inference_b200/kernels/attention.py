@@ -86,10 +86,11 @@ def decode_splits(num_seqs: int, num_heads: int, nkv: int, head_dim: int, page_s
 
 
 def paged_attention(out: torch.Tensor, qkv: torch.Tensor, cache, batch, num_heads: int, scale: float, window: int | None,
-                    splits: int | None = None, sink: float | None = None) -> None:
+                    splits: int | None = None, sink: float | torch.Tensor | None = None) -> None:
     """Attention of every token of the step over its sequence's pages.  ``splits``: key runs per single-token
     sequence, if the caller fixed them (a recorded graph); otherwise chosen from this step's shape.  ``sink``: the
-    score of a term that is added to every softmax denominator and carries no value (None: no such term)."""
+    score of a term that is added to every softmax denominator and carries no value (None: no such term); a float32 tensor
+    gives a score per query head."""
     group = batch.group(cache.group)
     _, nkv, _, d = cache.k.shape
     if out.dtype != torch.bfloat16 or not ops.mma_head_dim_supported(d):

@@ -302,7 +302,7 @@ def paged_attention_simt(
     num_heads: int,
     scale: float,
     window: int | None = None,
-    sink: float | None = None,
+    sink: float | torch.Tensor | None = None,
 ) -> None:
     """Causal attention of every token over its sequence's pages, on CUDA cores.  ``sink``: see ``_sink``.
 
@@ -348,7 +348,7 @@ def paged_prefill_tc(
     scale: float,
     window: int | None = None,
     query_tiles: int = 0,
-    sink: float | None = None,
+    sink: float | torch.Tensor | None = None,
 ) -> None:
     """bfloat16 attention for prompt portions on tcgen05 tensor cores with TMA-fed pages
     (head size 64 or 128; page sizes 8, 16, 32, 64, 128).  Arguments as paged_attention_mma.
@@ -398,7 +398,7 @@ def paged_decode_tma(
     splits: int = 1,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
     max_kv_len: int = 0,
-    sink: float | None = None,
+    sink: float | torch.Tensor | None = None,
 ) -> None:
     """bfloat16 attention of single-token sequences whose keys and values arrive by TMA (head size
     64 or 128; page sizes 8, 16, 32, ...).  Arguments as paged_attention_mma with max_q_len = 1.
@@ -540,7 +540,7 @@ def paged_attention_mma(
     window: int | None = None,
     splits: int = 1,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
-    sink: float | None = None,
+    sink: float | torch.Tensor | None = None,
 ) -> None:
     """bfloat16 tensor-core attention for the sequences [seq0, seq0 + num_seqs) of a batch.
 
